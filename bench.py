@@ -1,0 +1,325 @@
+#!/usr/bin/env python3
+"""Benchmark of the fused Q/K RMSNorm + RoPE + causal GQA attention path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload C4|C5|C2] [--impl reference]
+
+A step is one pass of the operator (row-prepare of K + attention, two kernel
+launches, output and prepared-K buffers preallocated) over the named
+workload.  With N > 1 (launched by torch.distributed.run, one rank per GPU)
+the workload is sharded by KV-head group: every rank owns Hkv/N whole GQA
+groups, there is no collective on the data path, and the reported value is
+the whole job's FLOPs over the slowest rank's device time.
+
+Prints one JSON line (rank 0).  `--impl reference` times the CPU FP32 oracle
+(the reference's own CPU path for this operator) on the host cores instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+from kernelfuser_b200.inputs import WORKLOADS, make_workload_inputs  # noqa: E402
+from kernelfuser_b200.roofline import attention_flops, load_peaks, prepare_bytes  # noqa: E402
+from kernelfuser_b200.shard import head_shard, shard_inputs  # noqa: E402
+
+METRIC = "Fused QKnorm+RoPE+attn prefill TFLOP/s"
+UNIT = "TFLOP/s"
+DTYPE_NAME = {torch.bfloat16: "bf16", torch.float16: "fp16", torch.float32: "fp32"}
+
+
+# ----------------------------------------------------------------------------
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.thread.join(timeout=2)
+        sm, mx, power = [], [], []
+        reasons = set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for r in self.rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1])); mx.append(float(r[2])); power.append(float(r[3]))
+            except ValueError:
+                continue
+            for name, val in zip(names, r[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        busy = [c for c, p in zip(sm, power) if p > 0.5 * max(power)] or sm
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm), "power_w_max": max(power)}
+
+
+def physical_gpu_index(local: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        parts = [p for p in vis.split(",") if p.strip()]
+        if local < len(parts) and parts[local].strip().isdigit():
+            return int(parts[local])
+    return local
+
+
+# ----------------------------------------------------------------------------
+def cpu_oracle_rate(w, seconds_budget: float = 15.0, threads=None):
+    """Times the CPU FP32 oracle on a bounded sample (batch 1 of the workload)
+    and returns (TFLOP/s, threads, description)."""
+    from oracle import oracle as orc
+    if threads:
+        torch.set_num_threads(threads)
+    nthreads = torch.get_num_threads()
+    xs = make_workload_inputs(w, seed=0, B=1, dtype=torch.float32)
+    flops = attention_flops(1, w.Hq, w.S, w.D, w.causal)
+    orc.oracle_fp32(*xs, w.causal)  # warm-up
+    times = []
+    t_end = time.perf_counter() + seconds_budget
+    while len(times) < 3 or (time.perf_counter() < t_end and len(times) < 50):
+        t0 = time.perf_counter()
+        orc.oracle_fp32(*xs, w.causal)
+        times.append(time.perf_counter() - t0)
+    t = statistics.median(times)
+    desc = (f"{w.name} at B=1 (1/{w.B} of the batch), fp32 oracle, median of {len(times)} runs, "
+            f"{t * 1e3:.0f} ms per run")
+    return flops / t / 1e12, nthreads, desc
+
+
+def run_reference(args, w, rank):
+    """The reference arm: the CPU FP32 oracle on the host cores (rank 0 only)."""
+    if rank != 0:
+        return
+    from oracle import oracle as orc
+    nthreads = torch.get_num_threads()
+    xs = make_workload_inputs(w, seed=0, B=1, dtype=torch.float32)
+    flops = attention_flops(1, w.Hq, w.S, w.D, w.causal)
+    for _ in range(max(args.warmup, 1)):
+        orc.oracle_fp32(*xs, w.causal)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        orc.oracle_fp32(*xs, w.causal)
+    dt = (time.perf_counter() - t0) / args.steps
+    val = flops / dt / 1e12
+    sample = f"each step = {w.name} at B=1 (1/{w.B} of the batch) through the CPU FP32 oracle"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
+        "config": workload_config(w, args.gpus),
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": nthreads, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def workload_config(w, n):
+    return {"workload": f"{w.name}: B={w.B} S={w.S} Hq={w.Hq} Hkv={w.Hkv} D={w.D} causal theta={w.theta:g}",
+            "flops_convention": "2*B*Hq*S^2*D (causal)", "sharding": f"kv-head groups, {w.Hkv // n} per GPU",
+            "l2": "flushed between steps (256 MiB write); inputs also exceed L2",
+            "step": "row-prepare(K) + attention, buffers preallocated"}
+
+
+# ----------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="C4", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--variant", type=int, default=0)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
+
+    w = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference(args, w, rank)
+        return
+
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the operator has no CPU path")
+
+    import torch.distributed as dist
+    import kernelfuser_b200 as kf
+
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- inputs: generated once on the CPU from the seed, this rank's head groups only
+    sh = head_shard(w.Hq, w.Hkv, rank, world)
+    q, k, v, gq, gk, cos, sin = make_workload_inputs(w, seed=0)
+    q, k, v = shard_inputs(q, k, v, sh, contiguous=True)
+    host = [t.pin_memory() for t in (q, k, v)]
+    small = [t.to(dev) for t in (gq, gk, cos, sin)]
+    dq, dk, dv = (torch.empty_like(t, device=dev) for t in host)
+    for d, h in zip((dq, dk, dv), host):
+        d.copy_(h, non_blocking=True)
+    out = torch.empty_like(dq)
+    kn = torch.empty_like(dk)
+    host_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    torch.cuda.synchronize()
+
+    def op():
+        return kf.optimized_attention(dq, dk, dv, *small, causal=w.causal, eps=w.eps, out=out, kn=kn,
+                                      variant=args.variant)
+
+    def op_split(ev):
+        # same two launches, with an event between them to time each kernel
+        kf.prepare_rows(dk, small[1], small[2], small[3], eps=w.eps, out=kn)
+        ev.record()
+        kf.attention_forward(dq, kn, dv, small[0], small[2], small[3], out, causal=w.causal, eps=w.eps,
+                             variant=args.variant)
+
+    flops_total = attention_flops(w.B, w.Hq, w.S, w.D, w.causal)
+    flops_rank = flops_total / world
+
+    # ---- warm-up
+    for _ in range(args.warmup):
+        flush.zero_()
+        op()
+    torch.cuda.synchronize()
+    kf.check_status(dev)
+
+    # ---- timed region: K steps, device time of the operator only (flush excluded)
+    sampler = ClockSampler(physical_gpu_index(local))
+    if rank == 0:
+        sampler.start()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    barrier()
+    wall0 = time.perf_counter()
+    for i in range(args.steps):
+        flush.zero_()
+        ev[i][0].record()
+        op_split(ev[i][1])
+        ev[i][2].record()
+    barrier()
+    wall = time.perf_counter() - wall0
+    clocks = sampler.stop() if rank == 0 else None
+    kf.check_status(dev)
+    t_prep = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
+    t_attn = sum(e[1].elapsed_time(e[2]) for e in ev) / args.steps
+    t_step = sum(e[0].elapsed_time(e[2]) for e in ev) / args.steps
+    times = torch.tensor([t_step, t_prep, t_attn], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    t_step, t_prep, t_attn = (float(x) for x in times.tolist())
+
+    # ---- end to end: pinned host inputs -> device, operator, output -> pinned host
+    e2e_steps = max(args.e2e_steps, 1)
+
+    def e2e_step():
+        for d, h in zip((dq, dk, dv), host):
+            d.copy_(h, non_blocking=True)
+        op()
+        host_out.copy_(out, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    t_e2e = torch.tensor([e0.elapsed_time(e1) / e2e_steps], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t_e2e, op=dist.ReduceOp.MAX)
+    t_e2e = float(t_e2e.item())
+    kf.check_status(dev)
+    h2d = sum(t.numel() * t.element_size() for t in host)
+    d2h = host_out.numel() * host_out.element_size()
+
+    if rank == 0:
+        peaks = load_peaks(ROOT)
+        tag = "of measured" if peaks["source"] == "measured" else "of fallback"
+        value = flops_total / (t_step * 1e-3) / 1e12
+        attn_tf = flops_rank / (t_attn * 1e-3) / 1e12
+        prep_b = prepare_bytes(w.B, sh.n_kv, w.S, w.D)
+        prep_gbs = prep_b / (t_prep * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": t_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": DTYPE_NAME[w.dtype], "data": "synthetic",
+            "config": workload_config(w, world),
+            "pct_of_nominal_bf16_peak": 100.0 * value / (2250.0 * world),
+            "roofline": {"kernel": "attention", "bound": "tensor", "achieved": attn_tf, "peak": peaks["bf16_tflops"],
+                         "unit": "TFLOP/s", "frac": attn_tf / peaks["bf16_tflops"], "traffic": None,
+                         "peak_source": f"{tag} (cuBLAS bf16 burst)", "ms_per_launch": t_attn,
+                         "flops_per_launch": flops_rank},
+            "roofline_prepare": {"kernel": "prepare_rows(K)", "bound": "hbm", "achieved": prep_gbs,
+                                 "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": prep_gbs / peaks["hbm_gbs"],
+                                 "traffic": None, "peak_source": tag, "ms_per_launch": t_prep,
+                                 "bytes_per_launch": prep_b},
+            "e2e": {"value": flops_total / (t_e2e * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d * world,
+                    "d2h_bytes_per_step": d2h * world, "ms_per_step": t_e2e, "steps": e2e_steps},
+            "gpu_launches": 2 * args.steps,
+            "clocks": clocks,
+            "wall_s_timed_region": wall,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            val, cores, desc = cpu_oracle_rate(w)
+            line["cpu_baseline"] = {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc}
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

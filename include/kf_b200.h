@@ -1,0 +1,82 @@
+/* C ABI of libkf_b200: the B200 (sm_100a) implementation of KernelFuser's fused
+ * Q/K RMSNorm + RoPE + GQA attention path.
+ *
+ * The reference has no native code; its "FFI" for this path is the pair of
+ * Triton launches made by `launch_attention`
+ * (src/e1_rope_publication_v1.py:661-677).  Each entry point below names the
+ * reference launch it replaces.  All pointers are DEVICE pointers unless said
+ * otherwise; the library never allocates or frees device memory and never
+ * synchronises: every call enqueues work on the given stream and returns.
+ *
+ * Conventions
+ *   dtype      KF_BF16 or KF_FP16; every tensor of a call shares it.
+ *   layout     tensors are [B, H, S, D] with D contiguous; batch, head and
+ *              row strides are given in ELEMENTS and must be multiples of 8
+ *              (16 bytes), base pointers 16-byte aligned.  D is 128 or 256.
+ *   tables     cos/sin are contiguous [S, D]; pass NULL for both to skip RoPE.
+ *   status     optional device int32 (may be NULL only for kf_prepare_rows):
+ *              stays 0 on success; a kernel whose bounded wait expired writes
+ *              a positive code there and returns without hanging.
+ *   return     0 on success; a negative KF_E* code when an argument is
+ *              rejected on the host (nothing was launched);
+ *              kf_last_error() then describes the reason (thread-local).
+ */
+#ifndef KF_B200_H_
+#define KF_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KF_BF16 0
+#define KF_FP16 1
+
+#define KF_OK 0
+#define KF_EINVAL (-1)   /* bad shape / dtype / flag                     */
+#define KF_EALIGN (-2)   /* pointer or stride not 16-byte aligned        */
+#define KF_ECUDA (-3)    /* CUDA runtime / driver call failed            */
+#define KF_ENOSUP (-4)   /* device is not compute capability 10.x        */
+
+/* Library version (major*10000 + minor*100 + patch). */
+int kf_version(void);
+
+/* Message for the last non-zero return on this host thread. */
+const char* kf_last_error(void);
+
+/* Row prepare: y = RoPE(RMSNorm(x) * gamma) with position = row index s.
+ * Replaces `prepare_kernel` (src/e1_rope_publication_v1.py:586-605) as launched
+ * by `prepare_attention` (:652-658): called once for K (mode 'query'), and
+ * also for Q in mode 'unfused'.  Rounding follows `_rows` (:551-582);
+ * hf_norm = 1 rounds the normalised value before the gamma multiply,
+ * hf_norm = 0 is the single-rounding 'legacy' style. */
+int kf_prepare_rows(const void* x, void* y, const void* gamma, const void* cos_table, const void* sin_table,
+                    int B, int H, int S, int D, int dtype, int hf_norm, float eps,
+                    int64_t x_stride_b, int64_t x_stride_h, int64_t x_stride_s,
+                    int64_t y_stride_b, int64_t y_stride_h, int64_t y_stride_s,
+                    void* stream);
+
+/* Attention forward: out = softmax(scale * QN KN^T + mask) V with GQA head
+ * mapping kv_head = q_head / (Hq / Hkv).  Replaces `attention_v2_kernel`
+ * (src/e1_rope_publication_v1.py:609-649) as launched at :674-677.
+ * fuse_q = 1: q is the RAW query; its RMSNorm/gamma/RoPE (gamma_q, tables,
+ * eps, hf_norm) is applied in the kernel prologue (mode 'query').
+ * fuse_q = 0: q is already prepared (mode 'unfused').
+ * kn is the prepared K from kf_prepare_rows; v is the raw V.
+ * scale is the softmax scale (the reference passes D^-0.5).
+ * variant: 0 = choose automatically, 1 = baseline kernel, 2 = pipelined kernel. */
+int kf_attention_fwd(const void* q, const void* kn, const void* v, const void* gamma_q,
+                     const void* cos_table, const void* sin_table, void* out,
+                     int B, int Hq, int Hkv, int S, int D, int dtype,
+                     int causal, int hf_norm, int fuse_q, float eps, float scale,
+                     int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
+                     int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_s,
+                     int64_t v_stride_b, int64_t v_stride_h, int64_t v_stride_s,
+                     int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s,
+                     int* status, int variant, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KF_B200_H_ */

@@ -1,0 +1,196 @@
+"""Operator API: ``optimized_attention`` and the runner-arm adapter ``fused``.
+
+Mirrors the reference's public operator
+(``optimized_attention``, src/e1_rope_publication_v1.py:680-726): the same
+positional/keyword signature, the same ``ValueError`` for every misuse it
+rejects (:695-719, with "compute capability 9" replaced by "10" and the dtype
+widened to bf16 or fp16), the same allocation pattern (``out`` and the
+prepared-K scratch via ``torch.empty_like``), two asynchronous launches on the
+current stream and no host synchronisation.  Keyword-only extensions whose
+defaults reproduce the reference: ``positions``/``theta`` (build the rotary
+tables as ``make_inputs`` does, :180-183), ``eps``, ``scale``, ``out``, ``kn``.
+
+The kernels live in libkf_b200.so (hand-written CUDA for sm_100a) and are
+reached through ctypes; there is no fallback path.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from .inputs import rope_tables
+
+_DTYPES = {torch.bfloat16: _lib.KF_BF16, torch.float16: _lib.KF_FP16}
+_status = {}  # device index -> int32[1] status word
+
+
+class KernelStatusError(RuntimeError):
+    """A kernel gave up on a bounded wait and reported a status code."""
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """The per-device int32 status word the kernels report into (0 = ok)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    t = _status.get(idx)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        _status[idx] = t
+    return t
+
+
+def check_status(device=None) -> None:
+    """Synchronise and raise if any kernel reported a failure on ``device``."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    w = status_word(dev)
+    code = int(w.item())
+    if code != 0:
+        w.zero_()
+        raise KernelStatusError(f"kernel reported status {code} (a bounded wait expired)")
+
+
+def _strides3(t: torch.Tensor):
+    return t.stride(0), t.stride(1), t.stride(2)
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _call(rc: int) -> None:
+    if rc != 0:
+        msg = _lib.last_error()
+        if rc in (-1, -2, -4):
+            raise ValueError(msg)
+        raise RuntimeError(f"libkf_b200 error {rc}: {msg}")
+
+
+def prepare_rows(x, gamma, cos=None, sin=None, *, norm_style="hf", eps=1e-6, out=None):
+    """RMSNorm + gamma + split-half RoPE of every row of ``x`` [B,H,S,D]
+    (position = row index).  The reference's ``prepare_attention``
+    (src/e1_rope_publication_v1.py:652-658) for one tensor."""
+    lib = _lib.load()
+    b, h, s, d = x.shape
+    y = torch.empty_like(x) if out is None else out
+    with torch.cuda.device(x.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        _call(lib.kf_prepare_rows(_ptr(x), _ptr(y), _ptr(gamma), _ptr(cos), _ptr(sin), b, h, s, d,
+                                  _DTYPES[x.dtype], int(norm_style == "hf"), float(eps),
+                                  *_strides3(x), *_strides3(y), stream))
+    return y
+
+
+def attention_forward(q, kn, v, gq, cos, sin, out, *, causal, norm_style="hf", fuse_q=True, eps=1e-6,
+                      scale=None, variant=0):
+    """Launch the attention kernel on prepared K (``kn``); see kf_attention_fwd."""
+    lib = _lib.load()
+    b, hq, s, d = q.shape
+    hkv = kn.shape[1]
+    sc = float(d ** -0.5 if scale is None else scale)
+    with torch.cuda.device(q.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        st = status_word(q.device)
+        _call(lib.kf_attention_fwd(_ptr(q), _ptr(kn), _ptr(v), _ptr(gq), _ptr(cos), _ptr(sin), _ptr(out),
+                                   b, hq, hkv, s, d, _DTYPES[q.dtype], int(bool(causal)),
+                                   int(norm_style == "hf"), int(bool(fuse_q)), float(eps), sc,
+                                   *_strides3(q), *_strides3(kn), *_strides3(v), *_strides3(out),
+                                   st.data_ptr(), int(variant), stream))
+    return out
+
+
+def _validate(q, k, v, gq, gk, cos, sin, mode, bn, norm_style, require_contiguous=True):
+    # Same predicates, in the same order, as the reference (:695-719).
+    if mode not in ("query", "unfused") or bn not in (64, 128):
+        raise ValueError("Expected query/unfused mode and BN=64/128")
+    if norm_style not in ("hf", "legacy"):
+        raise ValueError("Expected hf or legacy norm_style")
+    if (cos is None) != (sin is None):
+        raise ValueError("Provide both rotary tables or neither")
+    rotary = cos is not None
+    tensors = (q, k, v, gq, gk) + ((cos, sin) if rotary else ())
+    if any(t.requires_grad for t in tensors):
+        raise ValueError("This API is forward-only")
+    if q.ndim != 4 or k.ndim != 4 or k.shape != v.shape:
+        raise ValueError("Expected Q [B,Hq,S,D] and K/V [B,Hkv,S,D]")
+    b, h, s, d = q.shape
+    if (d not in (128, 256) or min(b, h, s) < 1 or k.shape[0] != b or
+            tuple(k.shape[2:]) != (s, d) or k.shape[1] < 1 or h % k.shape[1]):
+        raise ValueError("Expected D=128/256, matching batch/sequence and valid GQA")
+    if tuple(gq.shape) != (d,) or tuple(gk.shape) != (d,) or (
+            rotary and (tuple(cos.shape) != (s, d) or tuple(sin.shape) != (s, d))):
+        raise ValueError("Expected gamma [D] and optional rotary tables [S,D]")
+    if (q.dtype not in _DTYPES or
+            any(not t.is_cuda or t.device != q.device or t.dtype != q.dtype for t in tensors) or
+            (require_contiguous and any(not t.is_contiguous() for t in tensors))):
+        raise ValueError("Inputs must be contiguous BF16 (or FP16) on one CUDA device")
+    if torch.cuda.get_device_capability(q.device)[0] != 10:
+        raise ValueError("This implementation is written for SM100/Blackwell")
+    return rotary
+
+
+def optimized_attention(q, k, v, gq, gk, cos=None, sin=None, *, causal=False,
+                        mode="query", bn=128, gather=False, norm_style="hf",
+                        positions=None, theta=None, eps=1e-6, scale=None, out=None, kn=None,
+                        variant=0):
+    """Forward attention with per-head Q/K RMSNorm and optional split-half RoPE.
+
+    ``mode='query'`` prepares K once, then fuses Q normalisation and rotation
+    into the attention prologue (no normalised-Q tensor is written);
+    ``mode='unfused'`` prepares both Q and K first.  Pass both ``cos`` and
+    ``sin`` [S, D] to enable RoPE, or ``positions`` [S] with ``theta`` to have
+    the tables built here.  ``norm_style='hf'`` rounds the normalised
+    activation before the gamma multiply; ``'legacy'`` rounds once after the
+    fp32 product.  ``bn`` and ``gather`` are accepted and validated for
+    compatibility with the reference signature
+    (src/e1_rope_publication_v1.py:680-681); they select Triton tiling details
+    there and do not change the result.  ``out`` / ``kn`` let a caller supply
+    preallocated output and prepared-K scratch.
+    """
+    if positions is not None or theta is not None:
+        if positions is None or theta is None or cos is not None or sin is not None:
+            raise ValueError("Provide positions together with theta, and no tables")
+        cos, sin = rope_tables(positions.to(q.device), q.shape[-1], float(theta), q.dtype)
+    _validate(q, k, v, gq, gk, cos, sin, mode, bn, norm_style)
+    if not (eps > 0):
+        raise ValueError("eps must be positive")
+    out = torch.empty_like(q) if out is None else out
+    kn = torch.empty_like(k) if kn is None else kn
+    if out.shape != q.shape or out.dtype != q.dtype or kn.shape != k.shape or kn.dtype != k.dtype:
+        raise ValueError("out / kn must match q / k in shape and dtype")
+    with torch.cuda.device(q.device):
+        prepare_rows(k, gk, cos, sin, norm_style=norm_style, eps=eps, out=kn)
+        if mode == "unfused":
+            qn = prepare_rows(q, gq, cos, sin, norm_style=norm_style, eps=eps)
+            attention_forward(qn, kn, v, gq, cos, sin, out, causal=causal, norm_style=norm_style,
+                              fuse_q=False, eps=eps, scale=scale, variant=variant)
+        else:
+            attention_forward(q, kn, v, gq, cos, sin, out, causal=causal, norm_style=norm_style,
+                              fuse_q=True, eps=eps, scale=scale, variant=variant)
+    return out
+
+
+def fused(q, k, v, gq, gk, cos, sin, causal, eps=1e-6, scale=None, norm_style="qwen3"):
+    """Runner-arm adapter with the signature of the reference's arms
+    (``fused``/``separate``/``vendor``/``compiled_fn``,
+    src/e1_rope_publication_v1.py:185-225).  Accepts [S,D], [B,S,D] or
+    [B,1,S,D] tables (the first broadcast slice is used, :192-200), an
+    explicit ``scale``/``eps``, and head-transposed (non-contiguous) q/k/v
+    views as produced by a model's ``view(...).transpose(1, 2)``."""
+    if cos is not None:
+        if cos.ndim == 4: cos = cos[:, 0]
+        if sin.ndim == 4: sin = sin[:, 0]
+        if cos.ndim == 3: cos = cos[0]
+        if sin.ndim == 3: sin = sin[0]
+        cos = cos.to(q.dtype).contiguous()
+        sin = sin.to(q.dtype).contiguous()
+    style = "legacy" if norm_style == "legacy" else "hf"
+    _validate(q, k, v, gq.contiguous(), gk.contiguous(), cos, sin, "query", 128, style, require_contiguous=False)
+    for t in (q, k, v):
+        if t.stride(3) != 1 or any(st % 8 for st in t.stride()[:3]):
+            raise ValueError("q/k/v need a contiguous head dimension and 16-byte aligned strides")
+    out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    kn = torch.empty(k.shape, dtype=k.dtype, device=k.device)
+    with torch.cuda.device(q.device):
+        prepare_rows(k, gk.contiguous(), cos, sin, norm_style=style, eps=eps, out=kn)
+        attention_forward(q, kn, v, gq.contiguous(), cos, sin, out, causal=causal, norm_style=style,
+                          fuse_q=True, eps=eps, scale=scale)
+    return out

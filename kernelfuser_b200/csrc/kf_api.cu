@@ -1,0 +1,196 @@
+// C-ABI entry points of libkf_b200 (declared in include/kf_b200.h): host-side
+// argument checks, TMA tensor-map encoding and kernel launches.  No device
+// allocation, no synchronisation, no exceptions across the boundary.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "../../include/kf_b200.h"
+#include "attn_fwd_basic.cuh"
+#include "prepare_rows.cuh"
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+bool stride_ok(int64_t s) { return s >= 0 && (s % 8) == 0; }
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn get_encode() {
+    static EncodeFn fn = nullptr;
+    if (fn) return fn;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+        return nullptr;
+    fn = reinterpret_cast<EncodeFn>(p);
+    return fn;
+}
+
+// 4-D map over a [B, H, S, D] tensor (D contiguous); box = 64 columns x 128
+// rows, 128-byte swizzle, out-of-range rows read as zero / are not written.
+int make_map(CUtensorMap* m, const void* base, int dtype, int B, int H, int S, int D, int64_t sb, int64_t sh,
+             int64_t ss) {
+    EncodeFn enc = get_encode();
+    if (!enc) return fail(KF_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)H, (cuuint64_t)B};
+    // a stride of 0 (size-1 dimension) is replaced by a valid dummy
+    auto st = [&](int64_t s, int64_t dflt) { return (cuuint64_t)((s > 0 ? s : dflt) * 2); };
+    cuuint64_t strides[3] = {st(ss, D), st(sh, (int64_t)S * D), st(sb, (int64_t)H * S * D)};
+    cuuint32_t box[4] = {64, 128, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(m, dtype == KF_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                     const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(KF_ECUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return KF_OK;
+}
+
+int check_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return fail(KF_ECUDA, "cudaGetDevice failed");
+    static int cached_major[64];
+    if (dev < 0 || dev >= 64) return fail(KF_ECUDA, "device ordinal %d out of range", dev);
+    if (cached_major[dev] == 0) {
+        int major = 0;
+        if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess)
+            return fail(KF_ECUDA, "cannot query the compute capability");
+        cached_major[dev] = major;
+    }
+    if (cached_major[dev] != 10) return fail(KF_ENOSUP, "this library is built for sm_100a (compute capability 10.x)");
+    return KF_OK;
+}
+
+int check_common(int B, int H, int S, int D, int dtype) {
+    if (dtype != KF_BF16 && dtype != KF_FP16) return fail(KF_EINVAL, "dtype must be KF_BF16 or KF_FP16");
+    if (D != 128 && D != 256) return fail(KF_EINVAL, "head dim must be 128 or 256 (got %d)", D);
+    if (B < 1 || H < 1 || S < 1) return fail(KF_EINVAL, "B, H and S must be >= 1 (got %d, %d, %d)", B, H, S);
+    return KF_OK;
+}
+
+template <int D, typename T> int launch_prepare(const kf::PrepareArgs& a, cudaStream_t st) {
+    constexpr int RPB = (32 / (D / 16)) * (kf::kPrepThreads / 32);
+    const int gx = (a.S + RPB - 1) / RPB;
+    kf::PrepareArgs args = a;
+    const int BH = a.B * a.H;
+    int gy = (148 * 8 + gx - 1) / gx;
+    if (gy < 1) gy = 1;
+    if (gy > BH) gy = BH;
+    int per = (BH + gy - 1) / gy;
+    per = ((per + kf::kPrepUnroll - 1) / kf::kPrepUnroll) * kf::kPrepUnroll;
+    gy = (BH + per - 1) / per;
+    if (gy > 65535) return fail(KF_EINVAL, "too many (batch, head) pairs");
+    args.bh_per_cta = per;
+    kf::prepare_rows_kernel<D, T><<<dim3(gx, gy), kf::kPrepThreads, 0, st>>>(args);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(KF_ECUDA, "prepare_rows launch failed: %s", cudaGetErrorString(e));
+    return KF_OK;
+}
+
+template <int D, typename T>
+int launch_attn_basic(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
+                      const kf::AttnArgs& a, cudaStream_t st) {
+    auto kern = kf::attn_fwd_basic_kernel<D, T>;
+    constexpr int smem = kf::attn_basic_smem_bytes<D>();
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return fail(KF_ECUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
+    const long long n_mblk = (a.S + kf::kBM - 1) / kf::kBM;
+    const long long grid = n_mblk * a.B * a.Hq;
+    if (grid > 0x7fffffffLL) return fail(KF_EINVAL, "too many tiles");
+    kern<<<(unsigned)grid, 128, smem, st>>>(mq, mk, mv, mo, a);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(KF_ECUDA, "attention launch failed: %s", cudaGetErrorString(e));
+    return KF_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int kf_version(void) { return 100; }
+
+const char* kf_last_error(void) { return g_err; }
+
+int kf_prepare_rows(const void* x, void* y, const void* gamma, const void* cos_table, const void* sin_table, int B,
+                    int H, int S, int D, int dtype, int hf_norm, float eps, int64_t x_sb, int64_t x_sh, int64_t x_ss,
+                    int64_t y_sb, int64_t y_sh, int64_t y_ss, void* stream) {
+    if (int r = check_common(B, H, S, D, dtype)) return r;
+    if (!x || !y || !gamma) return fail(KF_EINVAL, "x, y and gamma must not be NULL");
+    if ((cos_table == nullptr) != (sin_table == nullptr))
+        return fail(KF_EINVAL, "provide both rotary tables or neither");
+    if (!aligned16(x) || !aligned16(y) || !aligned16(gamma) || !aligned16(cos_table) || !aligned16(sin_table))
+        return fail(KF_EALIGN, "pointers must be 16-byte aligned");
+    if (!stride_ok(x_sb) || !stride_ok(x_sh) || !stride_ok(x_ss) || !stride_ok(y_sb) || !stride_ok(y_sh) ||
+        !stride_ok(y_ss))
+        return fail(KF_EALIGN, "strides must be non-negative multiples of 8 elements");
+    if (x_ss < D || y_ss < D) return fail(KF_EINVAL, "row stride must be at least D");
+    if (int r = check_device()) return r;
+    kf::PrepareArgs a{};
+    a.x = x; a.y = y; a.gamma = gamma; a.cos = cos_table; a.sin = sin_table;
+    a.x_sb = x_sb; a.x_sh = x_sh; a.x_ss = x_ss; a.y_sb = y_sb; a.y_sh = y_sh; a.y_ss = y_ss;
+    a.B = B; a.H = H; a.S = S; a.eps = eps; a.rope = cos_table != nullptr; a.hf_norm = hf_norm != 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (D == 128) return dtype == KF_BF16 ? launch_prepare<128, __nv_bfloat16>(a, st) : launch_prepare<128, __half>(a, st);
+    return dtype == KF_BF16 ? launch_prepare<256, __nv_bfloat16>(a, st) : launch_prepare<256, __half>(a, st);
+}
+
+int kf_attention_fwd(const void* q, const void* kn, const void* v, const void* gamma_q, const void* cos_table,
+                     const void* sin_table, void* out, int B, int Hq, int Hkv, int S, int D, int dtype, int causal,
+                     int hf_norm, int fuse_q, float eps, float scale, int64_t q_sb, int64_t q_sh, int64_t q_ss,
+                     int64_t k_sb, int64_t k_sh, int64_t k_ss, int64_t v_sb, int64_t v_sh, int64_t v_ss,
+                     int64_t o_sb, int64_t o_sh, int64_t o_ss, int* status, int variant, void* stream) {
+    if (int r = check_common(B, Hq, S, D, dtype)) return r;
+    if (Hkv < 1 || Hq % Hkv != 0) return fail(KF_EINVAL, "Hq (%d) must be a positive multiple of Hkv (%d)", Hq, Hkv);
+    if (!q || !kn || !v || !out || !status) return fail(KF_EINVAL, "q, kn, v, out and status must not be NULL");
+    if (fuse_q && !gamma_q) return fail(KF_EINVAL, "gamma_q is required when fuse_q is set");
+    if ((cos_table == nullptr) != (sin_table == nullptr))
+        return fail(KF_EINVAL, "provide both rotary tables or neither");
+    if (!aligned16(q) || !aligned16(kn) || !aligned16(v) || !aligned16(out) || !aligned16(gamma_q) ||
+        !aligned16(cos_table) || !aligned16(sin_table))
+        return fail(KF_EALIGN, "pointers must be 16-byte aligned");
+    const int64_t strides[12] = {q_sb, q_sh, q_ss, k_sb, k_sh, k_ss, v_sb, v_sh, v_ss, o_sb, o_sh, o_ss};
+    for (int64_t s : strides)
+        if (!stride_ok(s)) return fail(KF_EALIGN, "strides must be non-negative multiples of 8 elements");
+    if (q_ss < D || k_ss < D || v_ss < D || o_ss < D) return fail(KF_EINVAL, "row stride must be at least D");
+    if (!(scale > 0.f) || !(scale < 1e30f)) return fail(KF_EINVAL, "scale must be positive and finite");
+    if (variant < 0 || variant > 2) return fail(KF_EINVAL, "variant must be 0, 1 or 2");
+    if (int r = check_device()) return r;
+
+    CUtensorMap mq, mk, mv, mo;
+    if (int r = make_map(&mq, q, dtype, B, Hq, S, D, q_sb, q_sh, q_ss)) return r;
+    if (int r = make_map(&mk, kn, dtype, B, Hkv, S, D, k_sb, k_sh, k_ss)) return r;
+    if (int r = make_map(&mv, v, dtype, B, Hkv, S, D, v_sb, v_sh, v_ss)) return r;
+    if (int r = make_map(&mo, out, dtype, B, Hq, S, D, o_sb, o_sh, o_ss)) return r;
+
+    kf::AttnArgs a{};
+    a.gq = gamma_q; a.cos = cos_table; a.sin = sin_table;
+    a.B = B; a.Hq = Hq; a.Hkv = Hkv; a.S = S;
+    a.scale_log2e = scale * 1.4426950408889634f;
+    a.eps = eps; a.causal = causal != 0; a.rope = cos_table != nullptr; a.hf_norm = hf_norm != 0;
+    a.fuse_q = fuse_q != 0; a.status = status;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (D == 128)
+        return dtype == KF_BF16 ? launch_attn_basic<128, __nv_bfloat16>(mq, mk, mv, mo, a, st)
+                                : launch_attn_basic<128, __half>(mq, mk, mv, mo, a, st);
+    return dtype == KF_BF16 ? launch_attn_basic<256, __nv_bfloat16>(mq, mk, mv, mo, a, st)
+                            : launch_attn_basic<256, __half>(mq, mk, mv, mo, a, st);
+}
+
+}  // extern "C"

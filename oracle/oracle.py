@@ -1,0 +1,233 @@
+"""CPU oracle for the fused Q/K RMSNorm + RoPE + GQA attention path.
+
+TEST INFRASTRUCTURE ONLY.  Nothing in the product package imports this file;
+it is used by the tests, by the smoke check and by the CPU-baseline leg of the
+benchmark as the checker / the timed CPU baseline, never as a fallback for the
+CUDA kernels.
+
+Parity status: PINNED against outputs of the reference's own ``oracle_fp32``.
+The reference stores no golden vectors for this path, so the fixtures under
+``tests/golden/`` were produced by importing the reference module in a CPU
+container and running its ``oracle_fp32`` on seeded inputs
+(``tests/golden/make_golden.py`` is the generating script).
+
+Two independent things live here:
+
+1. ``oracle_fp32`` / ``oracle_fp32_explicit`` -- the FP32 oracle every arm of
+   the reference is judged against (src/e1_rope_publication_v1.py:295-302,
+   with helpers ``rope_torch(fp32=True)`` :141-168 and ``expand`` :170).  The
+   first form calls ``scaled_dot_product_attention`` exactly as the reference
+   does; the second spells the softmax out so the oracle does not depend on
+   a library attention kernel.
+2. ``emulate_rows`` / ``emulate_attention`` -- a CPU emulation of the
+   rounding contract of the reference's compiled (Triton) arm:
+   ``_rows`` (src/e1_rope_publication_v1.py:551-582) and the blocked
+   exp2 online softmax of ``attention_v2_kernel`` (:609-649).  The Triton
+   kernels cannot run without a GPU, so this emulation is the stand-in used
+   to bound "no worse than the reference's compiled arm".
+
+``metric`` restates the reference's acceptance gate
+(src/e1_rope_publication_v1.py:287-293) and adds the max-abs / mean-abs
+figures the build's tolerance is quoted in.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+EPS = 1e-6
+LOG2E = 1.4426950408889634
+
+
+# --------------------------------------------------------------------------
+# FP32 oracle
+# --------------------------------------------------------------------------
+def expand(x: torch.Tensor, h: int) -> torch.Tensor:
+    """GQA expansion: KV head g serves query heads g*G .. g*G+G-1
+    (src/e1_rope_publication_v1.py:170)."""
+    return x if x.shape[1] == h else x.repeat_interleave(h // x.shape[1], dim=1)
+
+
+def rmsnorm_fp32(x: torch.Tensor, gamma: torch.Tensor, eps: float = EPS) -> torch.Tensor:
+    """x * rsqrt(mean(x^2) + eps) * gamma, all in fp32
+    (src/e1_rope_publication_v1.py:298-299)."""
+    xf = x.float()
+    return xf * torch.rsqrt(xf.square().mean(-1, keepdim=True) + eps) * gamma.float()
+
+
+def rope_fp32(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """Split-half rotation in fp32 using only the FIRST half of the tables
+    (``rope_torch(fp32=True)``, src/e1_rope_publication_v1.py:141-168)."""
+    half = x.shape[-1] // 2
+    xx = x.float()
+    cc = cos.float()
+    ss = sin.float()
+    if cc.ndim == 2:
+        cc = cc[None, None]
+    elif cc.ndim == 3:
+        cc = cc[:, None]
+    if ss.ndim == 2:
+        ss = ss[None, None]
+    elif ss.ndim == 3:
+        ss = ss[:, None]
+    a, b = xx[..., :half], xx[..., half:]
+    c, s = cc[..., :half], ss[..., :half]
+    y = torch.empty_like(xx)
+    y[..., :half] = a * c - b * s
+    y[..., half:] = b * c + a * s
+    return y
+
+
+def _prepare_fp32(q, k, gq, gk, cos, sin, eps):
+    qn = rmsnorm_fp32(q, gq, eps)
+    kn = rmsnorm_fp32(k, gk, eps)
+    if cos is not None:
+        qn = rope_fp32(qn, cos, sin)
+        kn = rope_fp32(kn, cos, sin)
+    return qn, kn
+
+
+def oracle_fp32(q, k, v, gq, gk, cos=None, sin=None, causal=False, scale=None, eps=EPS):
+    """The reference's FP32 oracle (src/e1_rope_publication_v1.py:295-302).
+    ``cos is None`` gives the no-RoPE oracle of ``refinement_oracle``
+    (:735-742)."""
+    qn, kn = _prepare_fp32(q, k, gq, gk, cos, sin, eps)
+    h = q.shape[1]
+    return F.scaled_dot_product_attention(qn, expand(kn, h), expand(v.float(), h),
+                                          is_causal=causal, scale=scale)
+
+
+def oracle_fp32_explicit(q, k, v, gq, gk, cos=None, sin=None, causal=False, scale=None, eps=EPS):
+    """Same oracle with the softmax written out (no library attention call)."""
+    qn, kn = _prepare_fp32(q, k, gq, gk, cos, sin, eps)
+    h = q.shape[1]
+    s, d = q.shape[-2:]
+    sc = d ** -0.5 if scale is None else scale
+    z = torch.matmul(qn, expand(kn, h).transpose(-1, -2)) * sc
+    if causal:
+        keep = torch.ones(s, s, dtype=torch.bool).tril()
+        z = z.masked_fill(~keep, float("-inf"))
+    return torch.matmul(torch.softmax(z, dim=-1), expand(v.float(), h))
+
+
+# --------------------------------------------------------------------------
+# Rounding-contract emulation of the reference's compiled arm
+# --------------------------------------------------------------------------
+def emulate_rows(x, gamma, cos=None, sin=None, *, hf_norm=True, eps=EPS):
+    """``_rows`` (src/e1_rope_publication_v1.py:551-582) on CPU.
+
+    x: [..., S, D] in bf16/fp16; gamma [D]; cos/sin [S, D] in the same dtype.
+    Every ``r(.)`` below is a round-to-nearest-even to the input dtype, all
+    other arithmetic is fp32; the rotation uses the table entry of the OUTPUT
+    column j (both halves of the table are read, unlike the FP32 oracle).
+    """
+    dt = x.dtype
+    r = lambda t: t.to(dt).float()
+    d = x.shape[-1]
+    half = d // 2
+    xf = x.float()
+    inv = torch.rsqrt(xf.square().sum(-1, keepdim=True) / d + eps)
+    if hf_norm:
+        y = r(xf * inv)
+        y = r(y * gamma.to(dt).float())
+    else:
+        y = r(xf * inv * gamma.float())
+    if cos is not None:
+        partner = torch.cat([y[..., half:], y[..., :half]], dim=-1)
+        c = cos.to(dt).float()
+        s = sin.to(dt).float()
+        primary = r(y * c)
+        rotated = r(partner * s)
+        y = torch.cat([r(primary[..., :half] - rotated[..., :half]),
+                       r(primary[..., half:] + rotated[..., half:])], dim=-1)
+    return y.to(dt)
+
+
+def emulate_attention(qn, kn, v, causal=False, scale=None, bm=64, bn=128):
+    """Blocked exp2 online softmax of ``attention_v2_kernel``
+    (src/e1_rope_publication_v1.py:624-648): fp32 scores from 16-bit
+    operands, probabilities rounded to the input dtype for the PV product,
+    unrounded fp32 probabilities in the denominator, fp32 accumulation."""
+    dt = qn.dtype
+    b, h, s, d = qn.shape
+    hk = kn.shape[1]
+    g = h // hk
+    sc = (d ** -0.5 if scale is None else scale) * LOG2E
+    out = torch.empty_like(qn)
+    qf, kf, vf = qn.float(), kn.float(), v.float()
+    for m0 in range(0, s, bm):
+        m1 = min(m0 + bm, s)
+        q_t = qf[:, :, m0:m1]                                    # [B,H,bm,D]
+        acc = torch.zeros(b, h, m1 - m0, d)
+        mx = torch.full((b, h, m1 - m0), float("-inf"))
+        den = torch.zeros(b, h, m1 - m0)
+        end = min(m0 + bm, s) if causal else s
+        mi = torch.arange(m0, m1)
+        for n0 in range(0, end, bn):
+            n1 = min(n0 + bn, s)
+            k_t = expand(kf[:, :, n0:n1], h) if g > 1 else kf[:, :, n0:n1]
+            v_t = expand(vf[:, :, n0:n1], h) if g > 1 else vf[:, :, n0:n1]
+            z = torch.matmul(q_t, k_t.transpose(-1, -2)) * sc
+            if causal:
+                ni = torch.arange(n0, n1)
+                z = z.masked_fill(mi[:, None] < ni[None, :], float("-inf"))
+            new = torch.maximum(mx, z.max(-1).values)
+            alpha = torch.exp2(mx - new)
+            p = torch.exp2(z - new[..., None])
+            den = den * alpha + p.sum(-1)
+            acc = acc * alpha[..., None] + torch.matmul(p.to(dt).float(), v_t)
+            mx = new
+        out[:, :, m0:m1] = (acc / den[..., None]).to(dt)
+    return out
+
+
+def emulate_optimized_attention(q, k, v, gq, gk, cos=None, sin=None, *, causal=False,
+                                norm_style="hf", scale=None, eps=EPS, bn=128):
+    """CPU stand-in for ``optimized_attention(mode='query')``
+    (src/e1_rope_publication_v1.py:680-726): K-prepare, Q prologue and the
+    blocked attention with the compiled arm's rounding points."""
+    hf = norm_style == "hf"
+    kn = emulate_rows(k, gk, cos, sin, hf_norm=hf, eps=eps)
+    qn = emulate_rows(q, gq, cos, sin, hf_norm=hf, eps=eps)
+    return emulate_attention(qn, kn, v, causal=causal, scale=scale, bm=64, bn=bn)
+
+
+# --------------------------------------------------------------------------
+# Acceptance gate
+# --------------------------------------------------------------------------
+def metric(x: torch.Tensor, y: torch.Tensor, atol=0.025, rtol=0.025) -> dict:
+    """Candidate ``x`` against oracle ``y``: the reference gate
+    (finite, allclose(atol=rtol=.025), relative-L2 <= .025;
+    src/e1_rope_publication_v1.py:287-293) plus max-abs and mean-abs."""
+    a, b = x.float(), y.float()
+    finite = bool(torch.isfinite(a).all() and torch.isfinite(b).all())
+    diff = a - b
+    den = b.norm().clamp_min(1e-12)
+    rl2 = float(diff.norm() / den) if finite else float("inf")
+    close = bool(torch.allclose(a, b, atol=atol, rtol=rtol)) if finite else False
+    return {
+        "max_abs": float(diff.abs().max()) if finite else float("inf"),
+        "mean_abs": float(diff.abs().mean()) if finite else float("inf"),
+        "relative_l2": rl2,
+        "finite": finite,
+        "pass": bool(finite and close and rl2 <= 0.025),
+    }
+
+
+# Tolerances the build is held to (bf16; fp16 is tighter in practice but is
+# held to the same numbers): max-abs 2e-2 and mean-abs 2e-3 against the FP32
+# oracle, in addition to the reference gate above.
+MAX_ABS_TOL = 2e-2
+MEAN_ABS_TOL = 2e-3
+
+
+def within_tolerance(m: dict) -> bool:
+    return bool(m["pass"] and m["max_abs"] <= MAX_ABS_TOL and m["mean_abs"] <= MEAN_ABS_TOL)
+
+
+def attention_flops(b, hq, s, d, causal=True) -> float:
+    """Algorithmic FLOPs: 4*B*Hq*S^2*D dense, half of that when causal."""
+    f = 4.0 * b * hq * s * s * d
+    return f / 2 if causal else f
