@@ -67,11 +67,8 @@ __device__ __forceinline__ void q_prologue_inplace(uint8_t* smem_q, int r, int p
 #pragma unroll
     for (int bx = 0; bx < NB; ++bx) {
 #pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
-            float f[8];
-            unpack8<T>(*reinterpret_cast<const uint4*>(row + bx * kBoxBytes + ((ch ^ sw) << 4)), f);
-            ss = sumsq8(f, ss);
-        }
+        for (int ch = 0; ch < 8; ++ch)
+            ss = sumsq_chunk<T>(*reinterpret_cast<const uint4*>(row + bx * kBoxBytes + ((ch ^ sw) << 4)), ss);
     }
     const float inv = rsqrtf(ss * (1.0f / static_cast<float>(D)) + a.eps);
     const bool rope = a.rope != 0 && pos < a.S;
@@ -83,23 +80,17 @@ __device__ __forceinline__ void q_prologue_inplace(uint8_t* smem_q, int r, int p
     for (int c = 0; c < HC; ++c) {
         uint4* plo = reinterpret_cast<uint4*>(row + (c / 8) * kBoxBytes + (((c % 8) ^ sw) << 4));
         uint4* phi = reinterpret_cast<uint4*>(row + (c / 8 + NB / 2) * kBoxBytes + (((c % 8) ^ sw) << 4));
-        float lo[8], hi[8], glo[8], ghi[8], clo[8], chi[8], slo[8], shi[8];
-        unpack8<T>(*plo, lo);
-        unpack8<T>(*phi, hi);
-        unpack8<T>(__ldg(g4 + c), glo);
-        unpack8<T>(__ldg(g4 + HC + c), ghi);
+        uint4 lo = *plo, hi = *phi;
+        uint4 clo = make_uint4(0, 0, 0, 0), chi = clo, slo = clo, shi = clo;
         if (rope) {
-            unpack8<T>(__ldg(c4 + c), clo);
-            unpack8<T>(__ldg(c4 + HC + c), chi);
-            unpack8<T>(__ldg(s4 + c), slo);
-            unpack8<T>(__ldg(s4 + HC + c), shi);
-        } else {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) { clo[i] = chi[i] = 1.f; slo[i] = shi[i] = 0.f; }
+            clo = __ldg(c4 + c);
+            chi = __ldg(c4 + HC + c);
+            slo = __ldg(s4 + c);
+            shi = __ldg(s4 + HC + c);
         }
-        transform_pair<T>(lo, hi, inv, glo, ghi, clo, chi, slo, shi, hf, rope);
-        *plo = pack8<T>(lo);
-        *phi = pack8<T>(hi);
+        transform_pair<T>(lo, hi, inv, __ldg(g4 + c), __ldg(g4 + HC + c), clo, chi, slo, shi, hf, rope);
+        *plo = lo;
+        *phi = hi;
     }
 }
 

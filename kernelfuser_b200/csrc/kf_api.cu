@@ -90,7 +90,7 @@ template <int D, typename T> int launch_prepare(const kf::PrepareArgs& a, cudaSt
     const int gx = (a.S + RPB - 1) / RPB;
     kf::PrepareArgs args = a;
     const int BH = a.B * a.H;
-    int gy = (148 * 8 + gx - 1) / gx;
+    int gy = (148 * 16 + gx - 1) / gx;
     if (gy < 1) gy = 1;
     if (gy > BH) gy = BH;
     int per = (BH + gy - 1) / gy;

@@ -47,19 +47,15 @@ __global__ void __launch_bounds__(kPrepThreads) prepare_rows_kernel(const Prepar
     const bool rope = a.rope != 0, hf = a.hf_norm != 0;
 
     const uint4* g4 = reinterpret_cast<const uint4*>(a.gamma);
-    float glo[8], ghi[8], clo[8], chi[8], slo[8], shi[8];
-    unpack8<T>(__ldg(g4 + sub), glo);
-    unpack8<T>(__ldg(g4 + LPR + sub), ghi);
+    const uint4 glo = __ldg(g4 + sub), ghi = __ldg(g4 + LPR + sub);
+    uint4 clo = make_uint4(0, 0, 0, 0), chi = clo, slo = clo, shi = clo;
     if (rope && valid) {
         const uint4* c4 = reinterpret_cast<const uint4*>(a.cos) + static_cast<long long>(pos) * (D / 8);
         const uint4* s4 = reinterpret_cast<const uint4*>(a.sin) + static_cast<long long>(pos) * (D / 8);
-        unpack8<T>(__ldg(c4 + sub), clo);
-        unpack8<T>(__ldg(c4 + LPR + sub), chi);
-        unpack8<T>(__ldg(s4 + sub), slo);
-        unpack8<T>(__ldg(s4 + LPR + sub), shi);
-    } else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) { clo[i] = chi[i] = 1.f; slo[i] = shi[i] = 0.f; }
+        clo = __ldg(c4 + sub);
+        chi = __ldg(c4 + LPR + sub);
+        slo = __ldg(s4 + sub);
+        shi = __ldg(s4 + LPR + sub);
     }
 
     const int BH = a.B * a.H;
@@ -86,19 +82,16 @@ __global__ void __launch_bounds__(kPrepThreads) prepare_rows_kernel(const Prepar
 #pragma unroll
         for (int u = 0; u < kPrepUnroll; ++u) {
             const int p = bh + u;
-            float fl[8], fh[8];
-            unpack8<T>(lo[u], fl);
-            unpack8<T>(hi[u], fh);
-            float ss = sumsq8(fh, sumsq8(fl, 0.f));
+            float ss = sumsq_chunk<T>(hi[u], sumsq_chunk<T>(lo[u], 0.f));
 #pragma unroll
             for (int m = LPR / 2; m >= 1; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
             const float inv = rsqrtf(ss * (1.0f / static_cast<float>(D)) + a.eps);
-            transform_pair<T>(fl, fh, inv, glo, ghi, clo, chi, slo, shi, hf, rope);
+            transform_pair<T>(lo[u], hi[u], inv, glo, ghi, clo, chi, slo, shi, hf, rope);
             if (valid && p < bh1) {
                 const int b = p / a.H, h = p - b * a.H;
                 uint4* dst = reinterpret_cast<uint4*>(yb + b * a.y_sb + h * a.y_sh + pos * a.y_ss);
-                dst[sub] = pack8<T>(fl);
-                dst[LPR + sub] = pack8<T>(fh);
+                dst[sub] = lo[u];
+                dst[LPR + sub] = hi[u];
             }
         }
     }

@@ -1,5 +1,5 @@
 // The rounding contract of the row transform (RMSNorm -> gamma -> split-half
-// RoPE), shared by the K-prepare kernel and the attention kernel's Q prologue.
+// RoPE), shared by the row-prepare kernel and the attention kernel's Q prologue.
 //
 // Follows the reference's `_rows` (src/e1_rope_publication_v1.py:551-582):
 //   inv = rsqrt(sum(x^2)/D + eps)                        (fp32)
@@ -8,6 +8,11 @@
 //            out_j = r(r(y_j*cos_j) + r(p_j*sin_j))  for j >= D/2, p_j = y_{j-D/2}
 // where r(.) rounds to the 16-bit storage type (nearest even) and cos_j/sin_j
 // are the table entries of the OUTPUT column j.
+//
+// Every r(a op b) whose operands are already 16-bit values is ONE packed
+// 16-bit instruction (mul/add/sub .rn on bf16x2 / f16x2 round the exact result
+// once), so the contract costs about five instructions per element instead
+// of a convert round trip at every rounding point.
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -19,14 +24,28 @@ template <typename T> struct Num;
 template <> struct Num<__nv_bfloat16> {
     static constexpr uint32_t kFmt = 1;  // UMMA 16-bit format code
     __device__ static __forceinline__ float2 unpack(uint32_t u) {
-        // bf16 -> fp32 is a 16-bit shift
         return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xFFFF0000u));
     }
     __device__ static __forceinline__ uint32_t pack(float lo, float hi) {
-        __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-        return *reinterpret_cast<uint32_t*>(&v);
+        uint32_t r;
+        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+        return r;
     }
-    __device__ static __forceinline__ float round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+    __device__ static __forceinline__ uint32_t mul2(uint32_t a, uint32_t b) {
+        uint32_t r;
+        asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+        return r;
+    }
+    __device__ static __forceinline__ uint32_t add2(uint32_t a, uint32_t b) {
+        uint32_t r;
+        asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+        return r;
+    }
+    __device__ static __forceinline__ uint32_t sub2(uint32_t a, uint32_t b) {
+        uint32_t r;
+        asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+        return r;
+    }
 };
 template <> struct Num<__half> {
     static constexpr uint32_t kFmt = 0;
@@ -34,10 +53,25 @@ template <> struct Num<__half> {
         return __half22float2(*reinterpret_cast<__half2*>(&u));
     }
     __device__ static __forceinline__ uint32_t pack(float lo, float hi) {
-        __half2 v = __floats2half2_rn(lo, hi);
-        return *reinterpret_cast<uint32_t*>(&v);
+        uint32_t r;
+        asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+        return r;
     }
-    __device__ static __forceinline__ float round(float x) { return __half2float(__float2half_rn(x)); }
+    __device__ static __forceinline__ uint32_t mul2(uint32_t a, uint32_t b) {
+        uint32_t r;
+        asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+        return r;
+    }
+    __device__ static __forceinline__ uint32_t add2(uint32_t a, uint32_t b) {
+        uint32_t r;
+        asm("add.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+        return r;
+    }
+    __device__ static __forceinline__ uint32_t sub2(uint32_t a, uint32_t b) {
+        uint32_t r;
+        asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+        return r;
+    }
 };
 
 // 8 packed 16-bit values (one 16-byte chunk) <-> 8 floats
@@ -49,38 +83,51 @@ template <typename T> __device__ __forceinline__ uint4 pack8(const float (&f)[8]
     return make_uint4(Num<T>::pack(f[0], f[1]), Num<T>::pack(f[2], f[3]), Num<T>::pack(f[4], f[5]),
                       Num<T>::pack(f[6], f[7]));
 }
-__device__ __forceinline__ float sumsq8(const float (&f)[8], float acc) {
+// sum of squares of the 8 values of a chunk, accumulated into acc
+template <typename T> __device__ __forceinline__ float sumsq_chunk(const uint4& u, float acc) {
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc = fmaf(f[i], f[i], acc);
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = Num<T>::unpack(w[i]);
+        acc = fmaf(f.x, f.x, acc);
+        acc = fmaf(f.y, f.y, acc);
+    }
     return acc;
 }
 
-// Normalise one element (no rotation yet).
-template <typename T> __device__ __forceinline__ float norm1(float x, float inv, float g, bool hf) {
-    if (hf) return Num<T>::round(__fmul_rn(Num<T>::round(__fmul_rn(x, inv)), g));
-    return Num<T>::round(__fmul_rn(__fmul_rn(x, inv), g));
+// Normalise two packed elements: hf -> r(r(x*inv)*g); legacy -> r(x*inv*g).
+template <typename T> __device__ __forceinline__ uint32_t norm2(uint32_t x, float inv, uint32_t g, bool hf) {
+    const float2 f = Num<T>::unpack(x);
+    if (hf) return Num<T>::mul2(Num<T>::pack(__fmul_rn(f.x, inv), __fmul_rn(f.y, inv)), g);
+    const float2 gf = Num<T>::unpack(g);
+    return Num<T>::pack(__fmul_rn(__fmul_rn(f.x, inv), gf.x), __fmul_rn(__fmul_rn(f.y, inv), gf.y));
 }
 
-// Transform the chunk pair (lo: columns j..j+7 < D/2, hi: columns j+D/2..).
-// g*/c*/s* are the gamma and table chunks at the same columns.  In place.
+// Transform the chunk pair (lo: columns j..j+7 < D/2, hi: columns j+D/2..) in
+// place.  g*/c*/s* are the gamma and table chunks at the same columns.
 template <typename T>
-__device__ __forceinline__ void transform_pair(float (&lo)[8], float (&hi)[8], float inv, const float (&glo)[8],
-                                               const float (&ghi)[8], const float (&clo)[8], const float (&chi)[8],
-                                               const float (&slo)[8], const float (&shi)[8], bool hf, bool rope) {
+__device__ __forceinline__ void transform_pair(uint4& lo, uint4& hi, float inv, const uint4& glo, const uint4& ghi,
+                                               const uint4& clo, const uint4& chi, const uint4& slo,
+                                               const uint4& shi, bool hf, bool rope) {
+    uint32_t* l = reinterpret_cast<uint32_t*>(&lo);
+    uint32_t* h = reinterpret_cast<uint32_t*>(&hi);
+    const uint32_t* gl = reinterpret_cast<const uint32_t*>(&glo);
+    const uint32_t* gh = reinterpret_cast<const uint32_t*>(&ghi);
+    const uint32_t* cl = reinterpret_cast<const uint32_t*>(&clo);
+    const uint32_t* ch = reinterpret_cast<const uint32_t*>(&chi);
+    const uint32_t* sl = reinterpret_cast<const uint32_t*>(&slo);
+    const uint32_t* sh = reinterpret_cast<const uint32_t*>(&shi);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        float a = norm1<T>(lo[i], inv, glo[i], hf);
-        float b = norm1<T>(hi[i], inv, ghi[i], hf);
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t ya = norm2<T>(l[i], inv, gl[i], hf);
+        const uint32_t yb = norm2<T>(h[i], inv, gh[i], hf);
         if (rope) {
-            float pa = Num<T>::round(__fmul_rn(a, clo[i]));
-            float ra = Num<T>::round(__fmul_rn(b, slo[i]));
-            float pb = Num<T>::round(__fmul_rn(b, chi[i]));
-            float rb = Num<T>::round(__fmul_rn(a, shi[i]));
-            a = __fsub_rn(pa, ra);  // rounded to T by the final pack
-            b = __fadd_rn(pb, rb);
+            l[i] = Num<T>::sub2(Num<T>::mul2(ya, cl[i]), Num<T>::mul2(yb, sl[i]));
+            h[i] = Num<T>::add2(Num<T>::mul2(yb, ch[i]), Num<T>::mul2(ya, sh[i]));
+        } else {
+            l[i] = ya;
+            h[i] = yb;
         }
-        lo[i] = a;
-        hi[i] = b;
     }
 }
 
