@@ -24,6 +24,7 @@
 #ifndef KF_B200_H_
 #define KF_B200_H_
 
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -75,6 +76,35 @@ int kf_attention_fwd(const void* q, const void* kn, const void* v, const void* g
                      int64_t v_stride_b, int64_t v_stride_h, int64_t v_stride_s,
                      int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s,
                      int* status, int variant, void* stream);
+
+/* Whole operator without any allocation (no counterpart in the reference,
+ * whose wrapper always allocates its prepared-K scratch with torch.empty_like).
+ * For callers that cannot allocate device memory where they call from: hosts
+ * whose framework owns the device heap, code running while cudaMalloc is
+ * off-limits (it synchronises the device and is illegal during stream
+ * capture), request paths that must never enter the allocator.  The prepared K
+ * goes to a fixed array inside the library image, so every GPU that loads the
+ * library gives up kf_static_scratch_bytes() (32 MiB) until the process ends.
+ *   - Runs kf_prepare_rows on k into that array, then kf_attention_fwd with
+ *     fuse_q = 1; q/k/v/out/status are the caller's, as in those calls.
+ *   - B*Hkv*S*D*2 bytes must fit in the array, else KF_EINVAL (nothing runs).
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current); make that first call
+ *     outside any stream capture.
+ *   - All calls on a device share the one array and it keeps the previous
+ *     call's contents.  Each call rewrites every row it later reads, so no
+ *     clearing is needed, but two calls whose kernels can overlap on the GPU
+ *     (different streams, no ordering) race on it: serialise them. */
+size_t kf_static_scratch_bytes(void);
+int kf_optimized_attention_static(const void* q, const void* k, const void* v, const void* gamma_q,
+                                  const void* gamma_k, const void* cos_table, const void* sin_table, void* out,
+                                  int B, int Hq, int Hkv, int S, int D, int dtype,
+                                  int causal, int hf_norm, float eps, float scale,
+                                  int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
+                                  int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_s,
+                                  int64_t v_stride_b, int64_t v_stride_h, int64_t v_stride_s,
+                                  int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s,
+                                  int* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -15,7 +15,8 @@ PKG = Path(__file__).resolve().parent
 LIB_PATH = PKG / "libkf_b200.so"
 
 KF_BF16, KF_FP16 = 0, 1
-EXPORTS = ("kf_version", "kf_last_error", "kf_prepare_rows", "kf_attention_fwd")
+EXPORTS = ("kf_version", "kf_last_error", "kf_prepare_rows", "kf_attention_fwd",
+           "kf_static_scratch_bytes", "kf_optimized_attention_static")
 
 _lib = None
 
@@ -34,6 +35,11 @@ def _declare(lib):
     lib.kf_attention_fwd.restype = c_int
     lib.kf_attention_fwd.argtypes = ([c_void_p] * 7 + [c_int] * 9 + [c_float] * 2 + [c_int64] * 12 +
                                      [c_void_p, c_int, c_void_p])
+    lib.kf_static_scratch_bytes.restype = ctypes.c_size_t
+    lib.kf_static_scratch_bytes.argtypes = []
+    lib.kf_optimized_attention_static.restype = c_int
+    lib.kf_optimized_attention_static.argtypes = ([c_void_p] * 8 + [c_int] * 8 + [c_float] * 2 + [c_int64] * 12 +
+                                                  [c_void_p, c_void_p])
     return lib
 
 

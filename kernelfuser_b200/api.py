@@ -194,3 +194,32 @@ def fused(q, k, v, gq, gk, cos, sin, causal, eps=1e-6, scale=None, norm_style="q
         attention_forward(q, kn, v, gq.contiguous(), cos, sin, out, causal=causal, norm_style=style,
                           fuse_q=True, eps=eps, scale=scale)
     return out
+
+
+def optimized_attention_static(q, k, v, gq, gk, cos, sin, out, *, causal=False, norm_style="hf",
+                               eps=1e-6, scale=None):
+    """The whole operator through ``kf_optimized_attention_static``: the
+    prepared K goes to a fixed 32 MiB array inside the library instead of a
+    freshly allocated tensor, so this call allocates nothing (``out`` is the
+    caller's).  Meant for callers that cannot allocate device memory where
+    they call from (a host framework that owns the device heap, a section
+    where cudaMalloc is off-limits, a request path that must stay out of the
+    allocator).  ``B*Hkv*S*D*2`` bytes must fit in the array (``ValueError``
+    otherwise).  All calls on a device share that array: do not let two of
+    them overlap on the GPU.  The first call on a device looks up the array's
+    address and should be made outside any stream capture."""
+    lib = _lib.load()
+    _validate(q, k, v, gq, gk, cos, sin, "query", 128, norm_style)
+    if out.shape != q.shape or out.dtype != q.dtype or out.device != q.device or not out.is_contiguous():
+        raise ValueError("out must match q in shape, dtype and device and be contiguous")
+    b, hq, s, d = q.shape
+    sc = float(d ** -0.5 if scale is None else scale)
+    with torch.cuda.device(q.device):
+        st = status_word(q.device)
+        stream = torch.cuda.current_stream().cuda_stream
+        _call(lib.kf_optimized_attention_static(
+            _ptr(q), _ptr(k), _ptr(v), _ptr(gq), _ptr(gk), _ptr(cos), _ptr(sin), _ptr(out),
+            b, hq, k.shape[1], s, d, _DTYPES[q.dtype], int(bool(causal)), int(norm_style == "hf"),
+            float(eps), sc, *_strides3(q), *_strides3(k), *_strides3(v), *_strides3(out),
+            st.data_ptr(), stream))
+    return out

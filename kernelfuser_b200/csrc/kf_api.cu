@@ -194,3 +194,76 @@ int kf_attention_fwd(const void* q, const void* kn, const void* v, const void* g
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant of the whole operator.
+//
+// Some callers cannot allocate device memory at the moment they need the
+// operator: code that runs under a framework which owns the whole device heap
+// and hands out no raw allocations, plugins invoked from inside a region where
+// cudaMalloc is forbidden (it synchronises the device and is illegal while a
+// stream is being captured), or real-time serving loops that must not touch
+// the allocator on the request path.  For them the prepared-K scratch lives in
+// the fixed array below, which is part of the library image: every GPU that
+// loads the library reserves kStaticScratchBytes for it until the process
+// exits.
+constexpr size_t kStaticScratchBytes = 32u << 20;  // 32 MiB: B*Hkv*S*D*2 bytes must fit
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+namespace {
+// The array's name is only a host-side handle; kernels need its device address,
+// which differs per device and is looked up once per device (with that device
+// current) through cudaGetSymbolAddress.
+void* g_scratch_addr[64];
+bool g_scratch_ready[64];
+
+int static_scratch_for_current_device(void** out) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return fail(KF_ECUDA, "cudaGetDevice failed");
+    if (dev < 0 || dev >= 64) return fail(KF_ECUDA, "device ordinal %d out of range", dev);
+    if (!g_scratch_ready[dev]) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess || p == nullptr)
+            return fail(KF_ECUDA, "cudaGetSymbolAddress(static scratch) failed: %s", cudaGetErrorString(e));
+        g_scratch_addr[dev] = p;
+        g_scratch_ready[dev] = true;
+    }
+    *out = g_scratch_addr[dev];
+    return KF_OK;
+}
+}  // namespace
+
+extern "C" {
+
+size_t kf_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+int kf_optimized_attention_static(const void* q, const void* k, const void* v, const void* gamma_q,
+                                  const void* gamma_k, const void* cos_table, const void* sin_table, void* out,
+                                  int B, int Hq, int Hkv, int S, int D, int dtype, int causal, int hf_norm,
+                                  float eps, float scale, int64_t q_sb, int64_t q_sh, int64_t q_ss, int64_t k_sb,
+                                  int64_t k_sh, int64_t k_ss, int64_t v_sb, int64_t v_sh, int64_t v_ss,
+                                  int64_t o_sb, int64_t o_sh, int64_t o_ss, int* status, void* stream) {
+    if (int r = check_common(B, Hq, S, D, dtype)) return r;
+    if (Hkv < 1 || Hq % Hkv != 0) return fail(KF_EINVAL, "Hq (%d) must be a positive multiple of Hkv (%d)", Hq, Hkv);
+    const unsigned long long need = 2ull * (unsigned long long)B * Hkv * S * D;
+    if (need > kStaticScratchBytes)
+        return fail(KF_EINVAL,
+                    "prepared K needs %llu bytes (B*Hkv*S*D*2) but the built-in scratch holds %llu; "
+                    "use kf_prepare_rows + kf_attention_fwd with a caller-allocated buffer",
+                    need, (unsigned long long)kStaticScratchBytes);
+    void* kn = nullptr;
+    if (int r = static_scratch_for_current_device(&kn)) return r;
+    // prepared K is laid out contiguously [B, Hkv, S, D] at the start of the scratch;
+    // every row the attention kernel reads is rewritten by this call, so nothing
+    // needs clearing between calls.
+    const int64_t n_ss = D, n_sh = (int64_t)S * D, n_sb = (int64_t)Hkv * S * D;
+    if (int r = kf_prepare_rows(k, kn, gamma_k, cos_table, sin_table, B, Hkv, S, D, dtype, hf_norm, eps, k_sb, k_sh,
+                                k_ss, n_sb, n_sh, n_ss, stream))
+        return r;
+    return kf_attention_fwd(q, kn, v, gamma_q, cos_table, sin_table, out, B, Hq, Hkv, S, D, dtype, causal, hf_norm,
+                            /*fuse_q=*/1, eps, scale, q_sb, q_sh, q_ss, n_sb, n_sh, n_ss, v_sb, v_sh, v_ss, o_sb,
+                            o_sh, o_ss, status, /*variant=*/0, stream);
+}
+
+}  // extern "C"
