@@ -170,10 +170,14 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--variant", type=int, default=0)
+    ap.add_argument("--batch", type=int, default=0, help="override the workload batch (profiling on a smaller case)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
 
     w = WORKLOADS[args.workload]
+    if args.batch > 0:
+        import dataclasses
+        w = dataclasses.replace(w, B=args.batch, name=f"{w.name}(batch {args.batch})")
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -10,6 +10,7 @@
 
 #include "../../include/kf_b200.h"
 #include "attn_fwd_basic.cuh"
+#include "attn_fwd_ws.cuh"
 #include "prepare_rows.cuh"
 
 namespace {
@@ -120,6 +121,23 @@ int launch_attn_basic(const CUtensorMap& mq, const CUtensorMap& mk, const CUtens
     return KF_OK;
 }
 
+template <typename T>
+int launch_attn_ws(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
+                   const kf::AttnArgs& a, cudaStream_t st) {
+    auto kern = kf::attn_fwd_ws_kernel<T>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kf::kWsSmemBytes);
+    if (e != cudaSuccess) return fail(KF_ECUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
+    const int G = a.Hq / a.Hkv;
+    const long long n_mblk = (a.S + kf::kBM - 1) / kf::kBM;
+    const long long upg = (G % 2 == 0) ? n_mblk * (G / 2) : ((n_mblk + 1) / 2) * G;
+    const long long grid = upg * a.B * a.Hkv;
+    if (grid > 0x7fffffffLL) return fail(KF_EINVAL, "too many tiles");
+    kern<<<(unsigned)grid, kf::kWsThreads, kf::kWsSmemBytes, st>>>(mq, mk, mv, mo, a);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(KF_ECUDA, "attention launch failed: %s", cudaGetErrorString(e));
+    return KF_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -186,6 +204,10 @@ int kf_attention_fwd(const void* q, const void* kn, const void* v, const void* g
     a.eps = eps; a.causal = causal != 0; a.rope = cos_table != nullptr; a.hf_norm = hf_norm != 0;
     a.fuse_q = fuse_q != 0; a.status = status;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (D == 128 && variant != 1)
+        return dtype == KF_BF16 ? launch_attn_ws<__nv_bfloat16>(mq, mk, mv, mo, a, st)
+                                : launch_attn_ws<__half>(mq, mk, mv, mo, a, st);
+    if (variant == 2) return fail(KF_EINVAL, "the pipelined kernel supports head dim 128 only");
     if (D == 128)
         return dtype == KF_BF16 ? launch_attn_basic<128, __nv_bfloat16>(mq, mk, mv, mo, a, st)
                                 : launch_attn_basic<128, __half>(mq, mk, mv, mo, a, st);
