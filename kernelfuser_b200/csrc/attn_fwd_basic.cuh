@@ -36,6 +36,10 @@ struct AttnArgs {
     float eps;
     int causal, rope, hf_norm, fuse_q;
     int* status;  // device status word: 0 = ok, else first failure code
+#ifdef KF_PROFILE
+    long long* prof;  // per-role cycle counters of one CTA (profiling builds only)
+    int prof_block;
+#endif
 };
 
 enum : int {
@@ -92,6 +96,67 @@ __device__ __forceinline__ void q_prologue_inplace(uint8_t* smem_q, int r, int p
         *plo = lo;
         *phi = hi;
     }
+}
+
+// Cooperative Q prologue for a group of 128 threads (4 warps) on one swizzled
+// 128-row tile.  D/16 lanes share a row (each owns one 16-byte chunk and its
+// rotation partner), so a warp touches 32/(D/16) rows per step with coalesced
+// table reads; the table chunks of the first half of the rows are fetched
+// BEFORE `wait_q()` (which blocks until the raw tile has landed), so their
+// latency overlaps the Q copy.  Returns false if the wait failed.
+template <int D, typename T, typename WaitFn>
+__device__ __forceinline__ bool q_prologue_coop(uint8_t* smem_q, int gtid, int m0, const AttnArgs& a, WaitFn&& wait_q) {
+    constexpr int LPR = D / 16;              // lanes per row
+    constexpr int RPW = 32 / LPR;            // rows per warp step
+    constexpr int NIT = kBM / (4 * RPW);     // steps
+    constexpr int HALF = NIT / 2;
+    constexpr int NB = D / 64;
+    const int lane = gtid & 31, w = gtid >> 5;
+    const int sub = lane % LPR, rsub = lane / LPR;
+    const bool hf = a.hf_norm != 0;
+    const uint4* g4 = reinterpret_cast<const uint4*>(a.gq);
+    const uint4 glo = __ldg(g4 + sub), ghi = __ldg(g4 + LPR + sub);
+    uint4 tb[HALF][4];
+    auto load_tables = [&](int it0) {
+#pragma unroll
+        for (int i = 0; i < HALF; ++i) {
+            const int pos = m0 + (it0 + i) * 4 * RPW + w * RPW + rsub;
+            if (a.rope != 0 && pos < a.S) {
+                const uint4* c4 = reinterpret_cast<const uint4*>(a.cos) + static_cast<long long>(pos) * (D / 8);
+                const uint4* s4 = reinterpret_cast<const uint4*>(a.sin) + static_cast<long long>(pos) * (D / 8);
+                tb[i][0] = __ldg(c4 + sub);
+                tb[i][1] = __ldg(c4 + LPR + sub);
+                tb[i][2] = __ldg(s4 + sub);
+                tb[i][3] = __ldg(s4 + LPR + sub);
+            } else {
+                tb[i][0] = tb[i][1] = tb[i][2] = tb[i][3] = make_uint4(0, 0, 0, 0);
+            }
+        }
+    };
+    load_tables(0);
+    if (!wait_q()) return false;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        if (h == 1) load_tables(HALF);
+#pragma unroll
+        for (int i = 0; i < HALF; ++i) {
+            const int r = (h * HALF + i) * 4 * RPW + w * RPW + rsub;
+            const bool rope = a.rope != 0 && (m0 + r) < a.S;
+            uint8_t* row = smem_q + r * 128;
+            const int off = ((sub % 8) ^ (r & 7)) << 4;
+            uint4* plo = reinterpret_cast<uint4*>(row + (sub / 8) * kBoxBytes + off);
+            uint4* phi = reinterpret_cast<uint4*>(row + (sub / 8 + NB / 2) * kBoxBytes + off);
+            uint4 lo = *plo, hi = *phi;
+            float ss = sumsq_chunk<T>(hi, sumsq_chunk<T>(lo, 0.f));
+#pragma unroll
+            for (int m = LPR / 2; m >= 1; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
+            const float inv = rsqrtf(ss * (1.0f / static_cast<float>(D)) + a.eps);
+            transform_pair<T>(lo, hi, inv, glo, ghi, tb[i][0], tb[i][1], tb[i][2], tb[i][3], hf, rope);
+            *plo = lo;
+            *phi = hi;
+        }
+    }
+    return true;
 }
 
 template <int D, typename T>

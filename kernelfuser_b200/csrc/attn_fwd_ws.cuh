@@ -10,14 +10,21 @@
 //     blocks of one head;
 //   * warps 0-3 / 4-7: softmax + Q prologue + epilogue of tile 0 / tile 1
 //     (thread r <-> row r <-> TMEM lane r);  warp 8: TMA producer (K/V rings of
-//     two stages each, raw Q tiles);  warp 9: MMA issuer (one elected lane);
-//   * TMEM (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each; P (16-bit)
-//     overwrites its S and feeds O += P V as the TMEM A operand;
-//   * the issuer alternates tiles: PV0(j), QK0(j+1), PV1(j), QK1(j+1) - while
-//     one tile's rows are in softmax the tensor pipe works for the other;
+//     128-row tiles, raw Q tiles);  warps 9 / 10: MMA issuer of tile 0 / tile 1
+//     (one elected lane each - a tcgen05.mma takes ~45 clocks to issue from one
+//     thread, so one issuer cannot keep the pipe fed with 64-clock MMAs; the two
+//     tiles are independent except for releasing the shared K/V stages);
+//   * the KV loop advances in SUB-BLOCKS of 64 keys.  TMEM (512 columns) holds,
+//     per tile, two 64-column score buffers and a 128-column output:
+//     S0a S0b | S1a S1b | O0 | O1.  Because scores are double-buffered the issuer
+//     queues Q K^T of sub-block j+1 BEFORE it waits for the probabilities of
+//     sub-block j, so softmax never waits for the tensor pipe and runs
+//     back-to-back (throughput-bound, not latency-bound);
+//   * P (16-bit) overwrites the score buffer it came from and feeds O += P V as
+//     the TMEM A operand; V is an MN-major shared-memory B operand;
 //   * the running output is rescaled only when a row's maximum grew by more
 //     than 2^8 since the exponent base was last moved (exact after the final
-//     division; keeps tcgen05.ld/st of O off the critical path);
+//     division), and only then does softmax wait for the previous P V;
 //   * CTAs are ordered (batch, KV head) major, heaviest query block first, so
 //     CTAs resident together stream the same K/V through L2.  No cluster
 //     multicast anywhere.
@@ -31,14 +38,15 @@ namespace kf {
 
 enum : int {
     kStatusWsQFull = 201, kStatusWsQReady = 202, kStatusWsKFull = 203, kStatusWsVFull = 204, kStatusWsKEmpty = 205,
-    kStatusWsVEmpty = 206, kStatusWsSFull = 207, kStatusWsPReady = 208, kStatusWsODone = 209,
+    kStatusWsVEmpty = 206, kStatusWsSFull = 207, kStatusWsPReady = 208, kStatusWsODone = 209, kStatusWsPvDone = 210,
 };
 
-constexpr int kWsThreads = 320;
+constexpr int kWsThreads = 352;  // 8 softmax warps, 1 producer warp, 2 issuer warps
 constexpr int kWsStages = 2;
 constexpr int kWsTileBytes = 2 * kBoxBytes;  // 128 rows x 128 columns of 16-bit values
 constexpr int kWsSmemBytes = (2 + 2 * kWsStages) * kWsTileBytes + 1024 + 512;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
+constexpr int kSub = 64;                    // keys per sub-block
 
 __device__ __forceinline__ bool mbar_wait_abortable(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -63,8 +71,69 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     return r;
 }
 
+#ifdef KF_PROFILE
+#define KF_PROF_DECL long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long prof_t = clock64(); const long long prof_start = prof_t
+#define KF_PROF(slot) do { const long long _n = clock64(); prof_acc[slot] += _n - prof_t; prof_t = _n; } while (0)
+#define KF_PROF_FLUSH(role) do { if (a.prof != nullptr && blockIdx.x == a.prof_block) { prof_acc[7] = clock64() - prof_start; for (int _i = 0; _i < 8; ++_i) a.prof[(role) * 8 + _i] = prof_acc[_i]; } } while (0)
+#else
+#define KF_PROF_DECL do {} while (0)
+#define KF_PROF(slot) do {} while (0)
+#define KF_PROF_FLUSH(role) do {} while (0)
+#endif
+
+// ---- packed fp32 pairs (one instruction for two lanes of the FMA pipe)
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 f2_pack(float lo, float hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void f2_unpack(f32x2 v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 f2_fma(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ f32x2 f2_add(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ f32x2 f2_sub(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
+// 2^x for x <= 0 on the FMA pipe (relieves the MUFU unit, which would otherwise
+// limit the kernel): n = round(x), f = x - n in [-0.5, 0.5], 2^f by a cubic
+// (max relative error 7.5e-5, far below the 16-bit rounding of P), 2^n by an
+// integer add into the exponent field.  x is clamped at -125 so the exponent
+// never underflows (2^-125 stands in for the 0 of a masked score).
+__device__ __forceinline__ void exp2_poly2(float x0, float x1, float& p0, float& p1) {
+    const float kMagic = 12582912.f;  // 1.5 * 2^23: adding it rounds to an integer in the low mantissa bits
+    x0 = fmaxf(x0, -125.f);
+    x1 = fmaxf(x1, -125.f);
+    const f32x2 x = f2_pack(x0, x1);
+    const f32x2 fr = f2_add(x, f2_pack(kMagic, kMagic));
+    const f32x2 f = f2_sub(x, f2_sub(fr, f2_pack(kMagic, kMagic)));
+    f32x2 p = f2_fma(f, f2_pack(0.0551716685f, 0.0551716685f), f2_pack(0.2426111251f, 0.2426111251f));
+    p = f2_fma(f, p, f2_pack(0.6932609677f, 0.6932609677f));
+    p = f2_fma(f, p, f2_pack(0.9999280572f, 0.9999280572f));
+    float r0, r1, q0, q1;
+    f2_unpack(fr, r0, r1);
+    f2_unpack(p, q0, q1);
+    p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(r0) << 23));
+    p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(r1) << 23));
+}
+
+// Which pairs of a 32-pair sub-block row go through the polynomial (the rest use MUFU ex2).
+constexpr uint32_t kPolyPairMask = 0x88888888u;  // every 4th pair: 25 %
+
 struct WsTile {
-    int h, m0, nblk;
+    int h, m0, nsub;
 };
 
 template <typename T>
@@ -74,10 +143,18 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                    const AttnArgs a) {
     constexpr int D = 128;
     constexpr uint32_t kTmemCols = 512;
-    constexpr uint32_t kIdescQK = umma_idesc(Num<T>::kFmt, 0, kBM, kBN);
+    constexpr uint32_t kIdescQK = umma_idesc(Num<T>::kFmt, 0, kBM, 64 /* kSub */);
     constexpr uint32_t kIdescPV = umma_idesc(Num<T>::kFmt, 1, kBM, D);
 
     if (*reinterpret_cast<volatile int*>(a.status) != 0) return;  // an earlier CTA failed: drain quickly
+#ifdef KF_PROFILE
+    const long long kernel_entry = clock64();
+    long long pe[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    long long pe_t = kernel_entry;
+#define KF_PE(slot) do { const long long _n = clock64(); pe[slot] += _n - pe_t; pe_t = _n; } while (0)
+#else
+#define KF_PE(slot) do {} while (0)
+#endif
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -91,9 +168,9 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     uint64_t* k_empty = bars + 6;   // [stages]
     uint64_t* v_full = bars + 8;    // [stages]
     uint64_t* v_empty = bars + 10;  // [stages]
-    uint64_t* s_full = bars + 12;   // [2] issuer -> softmax group
-    uint64_t* p_ready = bars + 14;  // [2] softmax group -> issuer
-    uint64_t* o_done = bars + 16;   // [2] issuer -> softmax group (last PV complete)
+    uint64_t* s_full = bars + 12;   // [tile][buffer] issuer -> softmax group
+    uint64_t* p_ready = bars + 16;  // [tile][buffer] softmax group -> issuer (one arrival per warp)
+    uint64_t* pv_done = bars + 20;  // [tile] issuer -> softmax group, one phase per sub-block
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 24);
     volatile int* s_abort = reinterpret_cast<volatile int*>(bars + 25);
 
@@ -103,7 +180,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const int G = a.Hq / a.Hkv;
     const bool pair_heads = (G % 2) == 0;
     const int n_mblk = (a.S + kBM - 1) / kBM;
-    const int n_kv_all = (a.S + kBN - 1) / kBN;
+    const int n_sub_all = (a.S + kSub - 1) / kSub;
     WsTile tile[2];
     int b, kh;
     {
@@ -119,11 +196,12 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         for (int t = 0; t < 2; ++t) {
             tile[t].h = kh * G + (pair_heads ? 2 * sub + t : sub);
             tile[t].m0 = (pair_heads ? mslot : 2 * mslot + t) * kBM;
-            const int full = a.causal ? min((tile[t].m0 + kBM + kBN - 1) / kBN, n_kv_all) : n_kv_all;
-            tile[t].nblk = (tile[t].m0 < a.S) ? full : 0;
+            const int full = a.causal ? min((tile[t].m0 + kBM) / kSub, n_sub_all) : n_sub_all;
+            tile[t].nsub = (tile[t].m0 < a.S) ? full : 0;
         }
     }
-    const int n_loop = max(tile[0].nblk, tile[1].nblk);
+    const int n_sub = max(tile[0].nsub, tile[1].nsub);  // sub-blocks of 64 keys
+    const int n_loop = (n_sub + 1) / 2;                 // K/V tiles of 128 keys
 
     if (tid == 0) {
         prefetch_tensormap(&tm_q);
@@ -133,14 +211,16 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             mbar_init(q_full + i, 1);
-            mbar_init(q_ready + i, 128);
+            mbar_init(q_ready + i, 4);
             mbar_init(k_full + i, 1);
-            mbar_init(k_empty + i, 1);
+            mbar_init(k_empty + i, 2);  // one arrival per issuer
             mbar_init(v_full + i, 1);
-            mbar_init(v_empty + i, 1);
-            mbar_init(s_full + i, 1);
-            mbar_init(p_ready + i, 128);
-            mbar_init(o_done + i, 1);
+            mbar_init(v_empty + i, 2);
+            mbar_init(s_full + 2 * i, 1);
+            mbar_init(s_full + 2 * i + 1, 1);
+            mbar_init(p_ready + 2 * i, 4);
+            mbar_init(p_ready + 2 * i + 1, 4);
+            mbar_init(pv_done + i, 1);
         }
         *s_abort = 0;
         fence_mbar_init();
@@ -164,73 +244,102 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         const int t = warp >> 2;
         const int r = tid & 127;
         const WsTile tl = (t == 0) ? tile[0] : tile[1];
-        if (tl.nblk > 0) {
+        if (tl.nsub > 0) {
             uint8_t* my_q = smem_q + t * kWsTileBytes;
             const uint32_t lane_base = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
             const uint32_t col_s = t * 128, col_o = 256 + t * 128;
             const int row = tl.m0 + r;
             // ---- Q prologue
-            if (!mbar_wait_abortable(q_full + t, 0, s_abort)) fail = kStatusWsQFull;
-            if (!fail) {
-                if (a.fuse_q) q_prologue_inplace<D, T>(my_q, r, row, a);
-                fence_proxy_async_smem();
-                mbar_arrive(q_ready + t);
+            KF_PE(0);
+            {
+                auto wait_q = [&]() { return mbar_wait_abortable(q_full + t, 0, s_abort); };
+                const bool ok = a.fuse_q ? q_prologue_coop<D, T>(my_q, r, tl.m0, a, wait_q) : wait_q();
+                if (!ok) fail = kStatusWsQFull;
             }
+            KF_PE(1);
+            if (!fail) {
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(q_ready + t);
+            }
+            KF_PE(2);
             float m_used = -INFINITY, den = 0.f;
             const float c = a.scale_log2e;
-            for (int j = 0; j < tl.nblk && !fail; ++j) {
-                const int n0 = j * kBN;
-                if (!mbar_wait_abortable(s_full + t, j & 1, s_abort)) { fail = kStatusWsSFull; break; }
+            KF_PROF_DECL;
+            for (int jj = 0; jj < tl.nsub && !fail; ++jj) {
+                const int buf = jj & 1;
+                const int n0 = jj * kSub;
+                const uint32_t col_sb = col_s + buf * kSub;
+                if (!mbar_wait_abortable(s_full + 2 * t + buf, (jj >> 1) & 1, s_abort)) { fail = kStatusWsSFull; break; }
                 tc_fence_after();
-                uint32_t sr[4][32];
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) tmem_ld32(lane_base + col_s + q4 * 32, sr[q4]);
+                KF_PROF(0);
+                if (jj == 0) KF_PE(3);
+                uint32_t sr[2][32];
+                tmem_ld32(lane_base + col_sb, sr[0]);
+                tmem_ld32(lane_base + col_sb + 32, sr[1]);
                 tmem_wait_ld();
-                const bool need_mask = (n0 + kBN > a.S) || (a.causal && (n0 + kBN - 1 > tl.m0));
+                KF_PROF(1);
+                const bool need_mask = (n0 + kSub > a.S) || (a.causal && (n0 + kSub - 1 > tl.m0));
                 if (need_mask) {
 #pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4)
+                    for (int q2 = 0; q2 < 2; ++q2)
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
-                            const int n = n0 + q4 * 32 + i;
-                            if (n >= a.S || (a.causal && n > row)) sr[q4][i] = 0xff800000u;  // -inf
+                            const int n = n0 + q2 * 32 + i;
+                            if (n >= a.S || (a.causal && n > row)) sr[q2][i] = 0xff800000u;  // -inf
                         }
                 }
                 float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4)
+                for (int q2 = 0; q2 < 2; ++q2)
 #pragma unroll
                     for (int i = 0; i < 32; i += 4) {
-                        mx0 = max3(mx0, __uint_as_float(sr[q4][i]), __uint_as_float(sr[q4][i + 1]));
-                        mx1 = max3(mx1, __uint_as_float(sr[q4][i + 2]), __uint_as_float(sr[q4][i + 3]));
+                        mx0 = max3(mx0, __uint_as_float(sr[q2][i]), __uint_as_float(sr[q2][i + 1]));
+                        mx1 = max3(mx1, __uint_as_float(sr[q2][i + 2]), __uint_as_float(sr[q2][i + 3]));
                     }
                 const float m_blk = fmaxf(mx0, mx1) * c;
                 // move the exponent base only when the maximum grew by more than the threshold
                 const bool grow = m_blk > m_used + kRescaleThreshold;
                 float alpha = 1.f;
                 if (grow) {
-                    alpha = fast_exp2(m_used - m_blk);  // 0 on the first block
+                    alpha = fast_exp2(m_used - m_blk);  // 0 on the first sub-block
                     m_used = m_blk;
                     den *= alpha;
                 }
                 const float neg_m = -m_used;
-                float ps0 = 0.f, ps1 = 0.f;
+                const f32x2 c2 = f2_pack(c, c), nm2 = f2_pack(neg_m, neg_m);
+                f32x2 psum = f2_pack(0.f, 0.f);
+                KF_PROF(2);
 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
+                for (int q2 = 0; q2 < 2; ++q2) {
                     uint32_t pk[16];
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
-                        const float p0 = fast_exp2(fmaf(__uint_as_float(sr[q4][2 * i]), c, neg_m));
-                        const float p1 = fast_exp2(fmaf(__uint_as_float(sr[q4][2 * i + 1]), c, neg_m));
-                        ps0 += p0;
-                        ps1 += p1;
+                        float x0, x1, p0, p1;
+                        f2_unpack(f2_fma(f2_pack(__uint_as_float(sr[q2][2 * i]), __uint_as_float(sr[q2][2 * i + 1])), c2, nm2),
+                                  x0, x1);
+                        if ((kPolyPairMask >> (q2 * 16 + i)) & 1u) {
+                            exp2_poly2(x0, x1, p0, p1);
+                        } else {
+                            p0 = fast_exp2(x0);
+                            p1 = fast_exp2(x1);
+                        }
+                        psum = f2_add(psum, f2_pack(p0, p1));
                         pk[i] = Num<T>::pack(p0, p1);
                     }
-                    tmem_st16(lane_base + col_s + q4 * 16, pk);  // P overwrites S (already in registers)
+                    tmem_st16(lane_base + col_sb + q2 * 16, pk);  // P overwrites its S (already in registers)
                 }
+                float ps0, ps1;
+                f2_unpack(psum, ps0, ps1);
                 den += ps0 + ps1;
-                // S(j) complete implies PV(j-1) complete, so O may be touched here
-                if (j > 0 && __any_sync(0xffffffffu, grow)) {
+                KF_PROF(3);
+                // Track the completion of the previous P V every sub-block (normally long past):
+                // it keeps this group within one phase of pv_done, and O may only be touched
+                // after it.
+                if (jj > 0 && !mbar_wait_abortable(pv_done + t, (jj - 1) & 1, s_abort)) { fail = kStatusWsPvDone; break; }
+                KF_PROF(4);
+                if (jj > 0 && __any_sync(0xffffffffu, grow)) {
+                    tc_fence_after();
 #pragma unroll
                     for (int q4 = 0; q4 < D / 32; ++q4) {
                         uint32_t o[32];
@@ -241,12 +350,18 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                         tmem_st32(lane_base + col_o + q4 * 32, o);
                     }
                 }
+                KF_PROF(5);
                 tmem_wait_st();
                 tc_fence_before();
-                mbar_arrive(p_ready + t);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(p_ready + 2 * t + buf);
+                KF_PROF(6);
             }
+            if ((warp & 3) == 0 && lane == 0) KF_PROF_FLUSH(t);
             // ---- epilogue: O / den -> 16-bit -> swizzled smem (this tile's Q buffer) -> TMA store
-            if (!fail && !mbar_wait_abortable(o_done + t, 0, s_abort)) fail = kStatusWsODone;
+            KF_PE(7);
+            if (!fail && !mbar_wait_abortable(pv_done + t, (tl.nsub - 1) & 1, s_abort)) fail = kStatusWsODone;
+            KF_PE(4);
             if (!fail) {
                 tc_fence_after();
                 const float inv_den = 1.f / den;
@@ -270,6 +385,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                 }
                 fence_proxy_async_smem();
             }
+            KF_PE(5);
             if (fail) {
                 *s_abort = 1;
                 atomicCAS(a.status, 0, fail);
@@ -280,15 +396,19 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                 tma_store_4d(&tm_o, my_q, 0, tl.m0, tl.h, b);
                 tma_store_4d(&tm_o, my_q + kBoxBytes, 64, tl.m0, tl.h, b);
                 tma_store_commit();
-                tma_store_wait_all();
+                tma_store_wait_read();  // the buffer must outlive the copy's reads; the writes drain on their own
             }
+            KF_PE(6);
+#ifdef KF_PROFILE
+            if (tid == 0 && a.prof != nullptr && blockIdx.x == a.prof_block) { pe[7] = clock64() - kernel_entry; for (int i = 0; i < 8; ++i) a.prof[32 + i] = pe[i]; }
+#endif
         }
     } else if (warp == 8) {
         // =================================================== TMA producer
         if (lane == 0) {
 #pragma unroll
             for (int t = 0; t < 2; ++t) {
-                if (tile[t].nblk > 0) {
+                if (tile[t].nsub > 0) {
                     mbar_expect_tx(q_full + t, kWsTileBytes);
                     tma_load_4d(smem_q + t * kWsTileBytes, &tm_q, q_full + t, 0, tile[t].m0, tile[t].h, b);
                     tma_load_4d(smem_q + t * kWsTileBytes + kBoxBytes, &tm_q, q_full + t, 64, tile[t].m0, tile[t].h, b);
@@ -317,61 +437,84 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         // =================================================== MMA issuer
         if (lane == 0) {
             const uint32_t q_addr = smem_u32(smem_q), k_addr = smem_u32(smem_k), v_addr = smem_u32(smem_v);
-            auto issue_qk = [&](int t, int stage) {
-                const uint32_t qa = q_addr + t * kWsTileBytes, ka = k_addr + stage * kWsTileBytes;
+            // Descriptors are built once; walking a tile only adds constants to the low word
+            // (units of 16 bytes): +2 per 16-column K step inside a 64-column box, +1024 per box,
+            // +512 per 64-row half, +2048 per stage, +128 per 16 V rows.
+            const uint64_t qk_desc = umma_desc_sw128(0, 16, 1024);        // K-major operands (Q and K)
+            const uint64_t v_desc = umma_desc_sw128(0, kBoxBytes, 1024);  // MN-major operand (V)
+            const uint32_t qk_hi = static_cast<uint32_t>(qk_desc >> 32), v_hi = static_cast<uint32_t>(v_desc >> 32);
+            const uint32_t q_lo = static_cast<uint32_t>(qk_desc) | ((q_addr & 0x3FFFFu) >> 4);
+            const uint32_t k_lo = static_cast<uint32_t>(qk_desc) | ((k_addr & 0x3FFFFu) >> 4);
+            const uint32_t v_lo = static_cast<uint32_t>(v_desc) | ((v_addr & 0x3FFFFu) >> 4);
+            // S_t[buffer jj&1] = Q_t (K rows [64*jj, 64*jj+64))^T
+            auto issue_qk = [&](int t, int jj) {
+                const uint32_t qa = q_lo + t * (kWsTileBytes >> 4);
+                const uint32_t ka = k_lo + ((jj >> 1) % kWsStages) * (kWsTileBytes >> 4) + (jj & 1) * ((kSub * 128) >> 4);
+                const uint32_t d = tmem_base + t * 128 + (jj & 1) * kSub;
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
-                    const uint32_t off = (ks / 4) * kBoxBytes + (ks % 4) * 32;
-                    umma_ss(tmem_base + t * 128, umma_desc_sw128(qa + off, 16, 1024), umma_desc_sw128(ka + off, 16, 1024),
-                            kIdescQK, ks > 0);
+                    const uint32_t off = (ks / 4) * (kBoxBytes >> 4) + (ks % 4) * 2;
+                    umma_ss_lohi(d, qa + off, qk_hi, ka + off, qk_hi, kIdescQK, ks > 0 ? 1u : 0u);
                 }
             };
-            auto issue_pv = [&](int t, int stage, bool accumulate) {
-                const uint32_t va = v_addr + stage * kWsTileBytes;
+            // O_t += P_t[buffer jj&1] (V rows [64*jj, 64*jj+64))
+            auto issue_pv = [&](int t, int jj) {
+                const uint32_t va = v_lo + ((jj >> 1) % kWsStages) * (kWsTileBytes >> 4) + (jj & 1) * ((kSub * 128) >> 4);
+                const uint32_t d = tmem_base + 256 + t * 128;
+                const uint32_t pa = tmem_base + t * 128 + (jj & 1) * kSub;
+                umma_ts_lohi(d, pa, va, v_hi, kIdescPV, jj > 0 ? 1u : 0u);
 #pragma unroll
-                for (int ks = 0; ks < kBN / 16; ++ks) {
-                    umma_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + ks * 8,
-                            umma_desc_sw128(va + ks * 2048, kBoxBytes, 1024), kIdescPV, accumulate || ks > 0);
-                }
+                for (int ks = 1; ks < kSub / 16; ++ks) umma_ts_lohi(d, pa + ks * 8, va + ks * 128, v_hi, kIdescPV, 1u);
             };
-            // block 0 scores
-            if (n_loop > 0) {
-                if (!mbar_wait_abortable(k_full + 0, 0, s_abort)) fail = kStatusWsKFull;
-#pragma unroll
-                for (int t = 0; t < 2; ++t) {
-                    if (!fail && tile[t].nblk > 0) {
-                        if (!mbar_wait_abortable(q_ready + t, 0, s_abort)) { fail = kStatusWsQReady; break; }
-                        tc_fence_after();
-                        issue_qk(t, 0);
-                        umma_commit(s_full + t);
-                    }
+            KF_PROF_DECL;
+            const int t = warp - 9;
+            const int my_nsub = (t == 0) ? tile[0].nsub : tile[1].nsub;
+            // scores of sub-block 0
+            if (n_sub > 0 && !mbar_wait_abortable(k_full + 0, 0, s_abort)) fail = kStatusWsKFull;
+            if (my_nsub > 0) {
+                if (!fail && !mbar_wait_abortable(q_ready + t, 0, s_abort)) fail = kStatusWsQReady;
+                if (!fail) {
+                    tc_fence_after();
+                    issue_qk(t, 0);
+                    umma_commit(s_full + 2 * t);
                 }
-                if (!fail) umma_commit(k_empty + 0);
             }
-            for (int j = 0; j < n_loop && !fail; ++j) {
-                const int sv = j % kWsStages;
-                const int sk1 = (j + 1) % kWsStages;
-                if (!mbar_wait_abortable(v_full + sv, (j / kWsStages) & 1, s_abort)) { fail = kStatusWsVFull; break; }
-                if (j + 1 < n_loop &&
-                    !mbar_wait_abortable(k_full + sk1, ((j + 1) / kWsStages) & 1, s_abort)) { fail = kStatusWsKFull; break; }
-#pragma unroll
-                for (int t = 0; t < 2; ++t) {
-                    if (j < tile[t].nblk) {
-                        if (!mbar_wait_abortable(p_ready + t, j & 1, s_abort)) { fail = kStatusWsPReady; break; }
+            KF_PROF(0);
+            for (int jj = 0; jj < n_sub && !fail; ++jj) {
+                // ---- queue the scores of sub-block jj+1 (their buffer was released by P V of jj-1)
+                const int j1 = jj + 1;
+                if (j1 < n_sub) {
+                    const int st1 = (j1 >> 1) % kWsStages;
+                    // (waited for even when this tile has no work left, so that this issuer's
+                    // stage releases can never run a whole ring turn ahead of the other issuer's)
+                    if ((j1 & 1) == 0 &&
+                        !mbar_wait_abortable(k_full + st1, ((j1 >> 1) / kWsStages) & 1, s_abort)) { fail = kStatusWsKFull; break; }
+                    if (j1 < my_nsub) {
                         tc_fence_after();
-                        issue_pv(t, sv, j > 0);
-                        if (j + 1 < tile[t].nblk) {
-                            issue_qk(t, sk1);
-                            umma_commit(s_full + t);
-                        } else {
-                            umma_commit(o_done + t);
-                        }
+                        KF_PROF(0);
+                        issue_qk(t, j1);
+                        umma_commit(s_full + 2 * t + (j1 & 1));
                     }
+                    if ((j1 & 1) == 1) umma_commit(k_empty + st1);  // this tile is done with both halves of that K tile
+                    KF_PROF(1);
                 }
-                if (fail) break;
-                umma_commit(v_empty + sv);
-                if (j + 1 < n_loop) umma_commit(k_empty + sk1);
+                // ---- O += P V of sub-block jj
+                const int st0 = (jj >> 1) % kWsStages;
+                if ((jj & 1) == 0 &&
+                    !mbar_wait_abortable(v_full + st0, ((jj >> 1) / kWsStages) & 1, s_abort)) { fail = kStatusWsVFull; break; }
+                if (jj < my_nsub) {
+                    KF_PROF(2);
+                    if (!mbar_wait_abortable(p_ready + 2 * t + (jj & 1), (jj >> 1) & 1, s_abort)) { fail = kStatusWsPReady; break; }
+                    tc_fence_after();
+                    KF_PROF(3);
+                    issue_pv(t, jj);
+                    umma_commit(pv_done + t);
+                    KF_PROF(4);
+                }
+                if ((jj & 1) == 1 || jj == n_sub - 1) umma_commit(v_empty + st0);
+                KF_PROF(5);
             }
+            KF_PROF_FLUSH(2 + t);
             if (fail) {
                 *s_abort = 1;
                 atomicCAS(a.status, 0, fail);

@@ -140,6 +140,15 @@ int launch_attn_ws(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorM
 
 }  // namespace
 
+#ifdef KF_PROFILE
+static __device__ long long g_prof[64];
+static int g_prof_block = 0;
+extern "C" void kf_prof_set_block(int b) { g_prof_block = b; }
+extern "C" int kf_prof_read(long long* host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, g_prof, sizeof(long long) * 64);
+}
+#endif
+
 extern "C" {
 
 int kf_version(void) { return 100; }
@@ -203,6 +212,14 @@ int kf_attention_fwd(const void* q, const void* kn, const void* v, const void* g
     a.scale_log2e = scale * 1.4426950408889634f;
     a.eps = eps; a.causal = causal != 0; a.rope = cos_table != nullptr; a.hf_norm = hf_norm != 0;
     a.fuse_q = fuse_q != 0; a.status = status;
+#ifdef KF_PROFILE
+    {
+        void* pp = nullptr;
+        cudaGetSymbolAddress(&pp, g_prof);
+        a.prof = static_cast<long long*>(pp);
+        a.prof_block = g_prof_block;
+    }
+#endif
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (D == 128 && variant != 1)
         return dtype == KF_BF16 ? launch_attn_ws<__nv_bfloat16>(mq, mk, mv, mo, a, st)
