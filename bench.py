@@ -41,57 +41,83 @@ DTYPE_NAME = {torch.bfloat16: "bf16", torch.float16: "fp16", torch.float32: "fp3
 
 # ----------------------------------------------------------------------------
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples SM clock, power and clock-event (throttle) reasons of one GPU through
+    NVML from a background thread while the timed region runs.  Reading only:
+    nothing on the GPU is changed."""
 
-    def __init__(self, gpu_index: int):
-        self.gpu = gpu_index
-        self.rows = []
-        self.proc = None
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+               0x4: "sw_power_cap", 0x80: "hw_power_brake_slowdown"}
+
+    def __init__(self, torch_device_index: int, period_s: float = 0.002):
+        self.period = period_s
+        self.samples = []  # (time, sm_mhz, power_w, reasons_bitmask)
+        self.t0 = self.t1 = None
+        self._stop = threading.Event()
+        self.thread = None
+        self.handle = None
+        self.max_mhz = None
+        try:
+            import pynvml
+            self.nvml = pynvml
+            pynvml.nvmlInit()
+            uuid = str(torch.cuda.get_device_properties(torch_device_index).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            self.handle = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode() if hasattr(uuid, "encode") else uuid)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+        except Exception as e:  # pragma: no cover - depends on the box
+            self.err = f"nvml unavailable: {e}"
+            self.handle = None
+
+    def _loop(self):
+        nv = self.nvml
+        while not self._stop.is_set():
+            try:
+                mhz = float(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
+                try:
+                    power = nv.nvmlDeviceGetPowerUsage(self.handle) / 1000.0
+                except Exception:
+                    power = float("nan")
+                try:
+                    reasons = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle))
+                except Exception:
+                    reasons = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))
+                self.samples.append((time.perf_counter(), mhz, power, reasons))
+            except Exception:
+                pass
+            time.sleep(self.period)
 
     def start(self):
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
-                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
-        except OSError:
-            self.proc = None
+        if self.handle is None:
+            return
+        self.thread = threading.Thread(target=self._loop, daemon=True)
+        self.thread.start()
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+    def mark_begin(self):
+        self.t0 = time.perf_counter()
+
+    def mark_end(self):
+        self.t1 = time.perf_counter()
 
     def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
+        if self.handle is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [getattr(self, "err", "nvml unavailable")]}
+        self._stop.set()
         self.thread.join(timeout=2)
-        sm, mx, power = [], [], []
-        reasons = set()
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for r in self.rows:
-            if len(r) < 9:
-                continue
-            try:
-                sm.append(float(r[1])); mx.append(float(r[2])); power.append(float(r[3]))
-            except ValueError:
-                continue
-            for name, val in zip(names, r[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        busy = [c for c, p in zip(sm, power) if p > 0.5 * max(power)] or sm
-        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
-                "samples": len(sm), "power_w_max": max(power)}
+        inside = [s for s in self.samples if self.t0 is not None and self.t0 <= s[0] <= (self.t1 or 1e30)]
+        scope = "timed region"
+        if len(inside) < 3:  # a very short timed region: fall back to every sample taken under load (warm-up too)
+            inside = self.samples
+            scope = "warm-up + timed region"
+        if not inside:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["no samples"]}
+        mask = 0
+        for s in inside:
+            mask |= s[3]
+        reasons = sorted(name for bit, name in self.REASONS.items() if mask & bit)
+        powers = [s[2] for s in inside if s[2] == s[2]]
+        return {"sm_mhz": statistics.median(s[1] for s in inside), "sm_max_mhz": self.max_mhz, "reasons": reasons,
+                "samples": len(inside), "scope": scope, "power_w_max": max(powers) if powers else None}
 
 
 def physical_gpu_index(local: int) -> int:
@@ -233,7 +259,10 @@ def main():
     flops_total = attention_flops(w.B, w.Hq, w.S, w.D, w.causal)
     flops_rank = flops_total / world
 
-    # ---- warm-up
+    # ---- warm-up (the clock sampler already runs, so a short timed region still has samples under load)
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
     for _ in range(args.warmup):
         flush.zero_()
         op()
@@ -241,11 +270,10 @@ def main():
     kf.check_status(dev)
 
     # ---- timed region: K steps, device time of the operator only (flush excluded)
-    sampler = ClockSampler(physical_gpu_index(local))
-    if rank == 0:
-        sampler.start()
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
     barrier()
+    if sampler:
+        sampler.mark_begin()
     wall0 = time.perf_counter()
     for i in range(args.steps):
         flush.zero_()
@@ -254,7 +282,9 @@ def main():
         ev[i][2].record()
     barrier()
     wall = time.perf_counter() - wall0
-    clocks = sampler.stop() if rank == 0 else None
+    if sampler:
+        sampler.mark_end()
+    clocks = sampler.stop() if sampler else None
     kf.check_status(dev)
     t_prep = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
     t_attn = sum(e[1].elapsed_time(e[2]) for e in ev) / args.steps

@@ -15,6 +15,8 @@ reached through ctypes; there is no fallback path.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import _lib
@@ -22,6 +24,12 @@ from .inputs import rope_tables
 
 _DTYPES = {torch.bfloat16: _lib.KF_BF16, torch.float16: _lib.KF_FP16}
 _status = {}  # device index -> int32[1] status word
+
+
+def _default_variant() -> int:
+    """Kernel variant used when a call does not name one (0 = automatic);
+    the environment variable KF_B200_ATTN_VARIANT overrides it for experiments."""
+    return int(os.environ.get("KF_B200_ATTN_VARIANT", "0"))
 
 
 class KernelStatusError(RuntimeError):
@@ -93,7 +101,7 @@ def attention_forward(q, kn, v, gq, cos, sin, out, *, causal, norm_style="hf", f
                                    b, hq, hkv, s, d, _DTYPES[q.dtype], int(bool(causal)),
                                    int(norm_style == "hf"), int(bool(fuse_q)), float(eps), sc,
                                    *_strides3(q), *_strides3(kn), *_strides3(v), *_strides3(out),
-                                   st.data_ptr(), int(variant), stream))
+                                   st.data_ptr(), int(variant) if variant else _default_variant(), stream))
     return out
 
 

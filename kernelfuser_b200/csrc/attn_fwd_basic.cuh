@@ -10,8 +10,9 @@
 //   * Q/K/V tiles arrive by TMA (4-D maps over [B,H,S,D], 64-column boxes,
 //     128-byte swizzle, zero fill past the end of the sequence).
 //   * The raw Q tile is normalised and rotated IN PLACE in shared memory, in
-//     the swizzled layout the MMA descriptor expects - no normalised-Q tensor
-//     ever exists in global memory.
+//     the swizzled layout the MMA descriptor expects (cooperatively: D/16 lanes
+//     per row, coalesced table reads) - no normalised-Q tensor ever exists in
+//     global memory.
 //   * S = Q K^T : tcgen05.mma, A and B from shared memory (K-major),
 //     accumulator in TMEM columns [0,128).
 //   * P (16-bit) is written back over S in TMEM and used as the A operand of
@@ -60,56 +61,18 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
-// In-place Q prologue on the swizzled shared-memory tile; thread r <-> row r.
-template <int D, typename T>
-__device__ __forceinline__ void q_prologue_inplace(uint8_t* smem_q, int r, int pos, const AttnArgs& a) {
-    constexpr int NB = D / 64;   // boxes per tile
-    constexpr int HC = D / 16;   // chunks per half row
-    uint8_t* row = smem_q + r * 128;
-    const int sw = r & 7;
-    float ss = 0.f;
-#pragma unroll
-    for (int bx = 0; bx < NB; ++bx) {
-#pragma unroll
-        for (int ch = 0; ch < 8; ++ch)
-            ss = sumsq_chunk<T>(*reinterpret_cast<const uint4*>(row + bx * kBoxBytes + ((ch ^ sw) << 4)), ss);
-    }
-    const float inv = rsqrtf(ss * (1.0f / static_cast<float>(D)) + a.eps);
-    const bool rope = a.rope != 0 && pos < a.S;
-    const bool hf = a.hf_norm != 0;
-    const uint4* g4 = reinterpret_cast<const uint4*>(a.gq);
-    const uint4* c4 = reinterpret_cast<const uint4*>(a.cos) + static_cast<long long>(pos) * (D / 8);
-    const uint4* s4 = reinterpret_cast<const uint4*>(a.sin) + static_cast<long long>(pos) * (D / 8);
-#pragma unroll 4
-    for (int c = 0; c < HC; ++c) {
-        uint4* plo = reinterpret_cast<uint4*>(row + (c / 8) * kBoxBytes + (((c % 8) ^ sw) << 4));
-        uint4* phi = reinterpret_cast<uint4*>(row + (c / 8 + NB / 2) * kBoxBytes + (((c % 8) ^ sw) << 4));
-        uint4 lo = *plo, hi = *phi;
-        uint4 clo = make_uint4(0, 0, 0, 0), chi = clo, slo = clo, shi = clo;
-        if (rope) {
-            clo = __ldg(c4 + c);
-            chi = __ldg(c4 + HC + c);
-            slo = __ldg(s4 + c);
-            shi = __ldg(s4 + HC + c);
-        }
-        transform_pair<T>(lo, hi, inv, __ldg(g4 + c), __ldg(g4 + HC + c), clo, chi, slo, shi, hf, rope);
-        *plo = lo;
-        *phi = hi;
-    }
-}
-
 // Cooperative Q prologue for a group of 128 threads (4 warps) on one swizzled
 // 128-row tile.  D/16 lanes share a row (each owns one 16-byte chunk and its
 // rotation partner), so a warp touches 32/(D/16) rows per step with coalesced
-// table reads; the table chunks of the first half of the rows are fetched
+// table reads; the table chunks of the first batch of rows are fetched
 // BEFORE `wait_q()` (which blocks until the raw tile has landed), so their
 // latency overlaps the Q copy.  Returns false if the wait failed.
-template <int D, typename T, typename WaitFn>
+template <int D, typename T, int HALVES = 2, typename WaitFn>
 __device__ __forceinline__ bool q_prologue_coop(uint8_t* smem_q, int gtid, int m0, const AttnArgs& a, WaitFn&& wait_q) {
     constexpr int LPR = D / 16;              // lanes per row
     constexpr int RPW = 32 / LPR;            // rows per warp step
     constexpr int NIT = kBM / (4 * RPW);     // steps
-    constexpr int HALF = NIT / 2;
+    constexpr int HALF = NIT / HALVES;       // steps whose table chunks are in flight together
     constexpr int NB = D / 64;
     const int lane = gtid & 31, w = gtid >> 5;
     const int sub = lane % LPR, rsub = lane / LPR;
@@ -136,8 +99,8 @@ __device__ __forceinline__ bool q_prologue_coop(uint8_t* smem_q, int gtid, int m
     load_tables(0);
     if (!wait_q()) return false;
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        if (h == 1) load_tables(HALF);
+    for (int h = 0; h < HALVES; ++h) {
+        if (h > 0) load_tables(h * HALF);
 #pragma unroll
         for (int i = 0; i < HALF; ++i) {
             const int r = (h * HALF + i) * 4 * RPW + w * RPW + rsub;
@@ -225,7 +188,7 @@ attn_fwd_basic_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     int fail = 0;
     int k_pending = 0, v_pending = 0;  // thread 0 only: a load was issued and not yet waited for
     int k_loads = 0, v_loads = 0;      // thread 0 only: loads issued so far
-    if (tid == 0) {
+    if (warp == 0 && elect_one()) {
         mbar_expect_tx(bar_q, kTileBytes);
 #pragma unroll
         for (int bx = 0; bx < NB; ++bx) tma_load_4d(smem_q + bx * kBoxBytes, &tm_q, bar_q, bx * 64, m0, h, b);
@@ -240,11 +203,12 @@ attn_fwd_basic_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     }
 
     // ---- Q prologue
-    if (!mbar_wait(bar_q, 0)) fail = kStatusWaitQ;
-    if (!fail) {
-        if (a.fuse_q) q_prologue_inplace<D, T>(smem_q, tid, m0 + tid, a);
-        fence_proxy_async_smem();
+    {
+        auto wait_q = [&]() { return mbar_wait(bar_q, 0); };
+        const bool ok = a.fuse_q ? q_prologue_coop<D, T, 4>(smem_q, tid, m0, a, wait_q) : wait_q();
+        if (!ok) fail = kStatusWaitQ;
     }
+    if (!fail) fence_proxy_async_smem();
     __syncthreads();
 
     float m_run = -INFINITY, den = 0.f;
@@ -255,7 +219,7 @@ attn_fwd_basic_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         const uint32_t ph = j & 1;
         const int n0 = j * kBN;
         // ---------------- S = Q K^T
-        if (tid == 0) {
+        if (warp == 0 && elect_one()) {
             if (!mbar_wait(bar_k, ph)) {
                 fail = kStatusWaitK;
             } else {
@@ -274,7 +238,7 @@ attn_fwd_basic_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         if (fail) break;
         if (!mbar_wait(bar_s, ph)) { fail = kStatusWaitS; break; }
         tc_fence_after();
-        if (tid == 0 && j + 1 < nblk) {  // K buffer is free again
+        if (warp == 0 && j + 1 < nblk && elect_one()) {  // K buffer is free again
             mbar_expect_tx(bar_k, kTileBytes);
 #pragma unroll
             for (int bx = 0; bx < NB; ++bx)
@@ -337,7 +301,7 @@ attn_fwd_basic_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         __syncthreads();
 
         // ---------------- O += P V
-        if (tid == 0) {
+        if (warp == 0 && elect_one()) {
             tc_fence_after();
             if (!mbar_wait(bar_v, ph)) {
                 fail = kStatusWaitV;
@@ -356,7 +320,7 @@ attn_fwd_basic_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         if (fail) break;
         if (!mbar_wait(bar_o, ph)) { fail = kStatusWaitO; break; }
         tc_fence_after();
-        if (tid == 0 && j + 1 < nblk) {  // V buffer (and S/P columns) are free again
+        if (warp == 0 && j + 1 < nblk && elect_one()) {  // V buffer (and S/P columns) are free again
             mbar_expect_tx(bar_v, kTileBytes);
 #pragma unroll
             for (int bx = 0; bx < NB; ++bx)
@@ -391,7 +355,7 @@ attn_fwd_basic_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     }
     tc_fence_before();
     __syncthreads();
-    if (tid == 0) {
+    if (warp == 0 && elect_one()) {
         if (!fail) {
 #pragma unroll
             for (int bx = 0; bx < NB; ++bx) tma_store_4d(&tm_o, smem_q + bx * kBoxBytes, bx * 64, m0, h, b);

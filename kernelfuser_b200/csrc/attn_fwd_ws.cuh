@@ -129,6 +129,45 @@ __device__ __forceinline__ void exp2_poly2(float x0, float x1, float& p0, float&
     p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(r1) << 23));
 }
 
+// The polynomial with the score scaling folded in.  The softmax's exponent base m is an
+// arbitrary float; the polynomial works from the nearest integer mi = rint(m) (so that
+// magic - mi is exact) and its coefficients carry the factor 2^(mi - m), which makes both
+// exp paths produce 2^(s*c - m):
+//   fr = s*c + (magic - mi)     -> n + magic, n = round(s*c - mi)     (one packed FMA)
+//   u  = (magic - mi) - fr      -> -(n + mi), exact
+//   f  = s*c + u                -> (s*c - mi) - n in [-0.5, 0.5]      (one packed FMA)
+//   p  = 2^(mi - m) * cubic(f) * 2^n
+// s is clamped from below at s_min = (mi - 125)/c, which keeps n >= -125 (no exponent
+// underflow) and turns a masked -inf score into ~2^-125.
+struct PolyBase {
+    f32x2 magic_minus_mi, k0, k1, k2, k3;
+    float s_min;
+    __device__ __forceinline__ void set(float m, float inv_c) {
+        const float mi = rintf(m);
+        const float k = fast_exp2(mi - m);
+        magic_minus_mi = f2_pack(12582912.f - mi, 12582912.f - mi);
+        k0 = f2_pack(0.9999280572f * k, 0.9999280572f * k);
+        k1 = f2_pack(0.6932609677f * k, 0.6932609677f * k);
+        k2 = f2_pack(0.2426111251f * k, 0.2426111251f * k);
+        k3 = f2_pack(0.0551716685f * k, 0.0551716685f * k);
+        s_min = (mi - 125.f) * inv_c;
+    }
+};
+__device__ __forceinline__ void exp2_poly2_scaled(float s0, float s1, f32x2 c2, const PolyBase& pb, float& p0,
+                                                  float& p1) {
+    const f32x2 sv = f2_pack(fmaxf(s0, pb.s_min), fmaxf(s1, pb.s_min));
+    const f32x2 fr = f2_fma(sv, c2, pb.magic_minus_mi);
+    const f32x2 f = f2_fma(sv, c2, f2_sub(pb.magic_minus_mi, fr));
+    f32x2 p = f2_fma(f, pb.k3, pb.k2);
+    p = f2_fma(f, p, pb.k1);
+    p = f2_fma(f, p, pb.k0);
+    float r0, r1, q0, q1;
+    f2_unpack(fr, r0, r1);
+    f2_unpack(p, q0, q1);
+    p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(r0) << 23));
+    p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(r1) << 23));
+}
+
 // Which pairs of a 32-pair sub-block row go through the polynomial (the rest use MUFU ex2).
 constexpr uint32_t kPolyPairMask = 0x88888888u;  // every 4th pair: 25 %
 
@@ -392,7 +431,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             }
             tc_fence_before();
             named_barrier_sync(1 + t, 128);
-            if (r == 0 && *s_abort == 0) {
+            if ((warp & 3) == 0 && elect_one() && *s_abort == 0) {
                 tma_store_4d(&tm_o, my_q, 0, tl.m0, tl.h, b);
                 tma_store_4d(&tm_o, my_q + kBoxBytes, 64, tl.m0, tl.h, b);
                 tma_store_commit();
@@ -405,7 +444,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         }
     } else if (warp == 8) {
         // =================================================== TMA producer
-        if (lane == 0) {
+        if (elect_one()) {
 #pragma unroll
             for (int t = 0; t < 2; ++t) {
                 if (tile[t].nsub > 0) {
@@ -435,7 +474,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         }
     } else {
         // =================================================== MMA issuer
-        if (lane == 0) {
+        if (elect_one()) {
             const uint32_t q_addr = smem_u32(smem_q), k_addr = smem_u32(smem_k), v_addr = smem_u32(smem_v);
             // Descriptors are built once; walking a tile only adds constants to the low word
             // (units of 16 bytes): +2 per 16-column K step inside a 64-column box, +1024 per box,
@@ -526,7 +565,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     __syncwarp();
     tc_fence_before();
     __syncthreads();
-    if (warp == 8 && lane == 0 && *s_abort != 0) {
+    if (warp == 8 && *s_abort != 0 && elect_one()) {
         // leave no copy in flight into this CTA's shared memory
 #pragma unroll
         for (int t = 0; t < 2; ++t)

@@ -11,6 +11,7 @@
 #include "../../include/kf_b200.h"
 #include "attn_fwd_basic.cuh"
 #include "attn_fwd_ws.cuh"
+#include "attn_fwd_persist.cuh"
 #include "prepare_rows.cuh"
 
 namespace {
@@ -44,17 +45,17 @@ EncodeFn get_encode() {
     return fn;
 }
 
-// 4-D map over a [B, H, S, D] tensor (D contiguous); box = 64 columns x 128
+// 4-D map over a [B, H, S, D] tensor (D contiguous); box = 64 columns x box_rows
 // rows, 128-byte swizzle, out-of-range rows read as zero / are not written.
 int make_map(CUtensorMap* m, const void* base, int dtype, int B, int H, int S, int D, int64_t sb, int64_t sh,
-             int64_t ss) {
+             int64_t ss, int box_rows = 128) {
     EncodeFn enc = get_encode();
     if (!enc) return fail(KF_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
     cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)H, (cuuint64_t)B};
     // a stride of 0 (size-1 dimension) is replaced by a valid dummy
     auto st = [&](int64_t s, int64_t dflt) { return (cuuint64_t)((s > 0 ? s : dflt) * 2); };
     cuuint64_t strides[3] = {st(ss, D), st(sh, (int64_t)S * D), st(sb, (int64_t)H * S * D)};
-    cuuint32_t box[4] = {64, 128, 1, 1};
+    cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult r = enc(m, dtype == KF_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
                      const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -138,14 +139,44 @@ int launch_attn_ws(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorM
     return KF_OK;
 }
 
+int sm_count() {
+    static int cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+template <typename T>
+int launch_attn_persist(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
+                        const kf::AttnArgs& a, cudaStream_t st) {
+    auto kern = kf::attn_fwd_persist_kernel<T>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kf::kPsSmemBytes);
+    if (e != cudaSuccess) return fail(KF_ECUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
+    const int G = a.Hq / a.Hkv;
+    const long long n_mblk = (a.S + kf::kBM - 1) / kf::kBM;
+    const long long upg = (G % 2 == 0) ? n_mblk * (G / 2) : ((n_mblk + 1) / 2) * G;
+    const long long items = upg * a.B * a.Hkv;
+    if (items > 0x7fffffffLL) return fail(KF_EINVAL, "too many tiles");
+    const int grid = (int)(items < sm_count() ? items : sm_count());
+    kern<<<grid, kf::kPsThreads, kf::kPsSmemBytes, st>>>(mq, mk, mv, mo, a, (int)items);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(KF_ECUDA, "attention launch failed: %s", cudaGetErrorString(e));
+    return KF_OK;
+}
+
 }  // namespace
 
 #ifdef KF_PROFILE
-static __device__ long long g_prof[64];
+static __device__ long long g_prof[2048];
 static int g_prof_block = 0;
 extern "C" void kf_prof_set_block(int b) { g_prof_block = b; }
 extern "C" int kf_prof_read(long long* host_out) {
-    return (int)cudaMemcpyFromSymbol(host_out, g_prof, sizeof(long long) * 64);
+    return (int)cudaMemcpyFromSymbol(host_out, g_prof, sizeof(long long) * 2048);
 }
 #endif
 
@@ -197,7 +228,7 @@ int kf_attention_fwd(const void* q, const void* kn, const void* v, const void* g
         if (!stride_ok(s)) return fail(KF_EALIGN, "strides must be non-negative multiples of 8 elements");
     if (q_ss < D || k_ss < D || v_ss < D || o_ss < D) return fail(KF_EINVAL, "row stride must be at least D");
     if (!(scale > 0.f) || !(scale < 1e30f)) return fail(KF_EINVAL, "scale must be positive and finite");
-    if (variant < 0 || variant > 2) return fail(KF_EINVAL, "variant must be 0, 1 or 2");
+    if (variant < 0 || variant > 3) return fail(KF_EINVAL, "variant must be 0..3");
     if (int r = check_device()) return r;
 
     CUtensorMap mq, mk, mv, mo;
@@ -221,10 +252,17 @@ int kf_attention_fwd(const void* q, const void* kn, const void* v, const void* g
     }
 #endif
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (D == 128 && variant != 1)
+    if (D == 128 && (variant == 0 || variant == 3)) {
+        CUtensorMap mk64, mv64;  // the persistent kernel streams K/V in 64-row tiles
+        if (int r = make_map(&mk64, kn, dtype, B, Hkv, S, D, k_sb, k_sh, k_ss, 64)) return r;
+        if (int r = make_map(&mv64, v, dtype, B, Hkv, S, D, v_sb, v_sh, v_ss, 64)) return r;
+        return dtype == KF_BF16 ? launch_attn_persist<__nv_bfloat16>(mq, mk64, mv64, mo, a, st)
+                                : launch_attn_persist<__half>(mq, mk64, mv64, mo, a, st);
+    }
+    if (D == 128 && variant == 2)
         return dtype == KF_BF16 ? launch_attn_ws<__nv_bfloat16>(mq, mk, mv, mo, a, st)
                                 : launch_attn_ws<__half>(mq, mk, mv, mo, a, st);
-    if (variant == 2) return fail(KF_EINVAL, "the pipelined kernel supports head dim 128 only");
+    if (variant >= 2) return fail(KF_EINVAL, "the pipelined kernels support head dim 128 only");  // D == 256 here
     if (D == 128)
         return dtype == KF_BF16 ? launch_attn_basic<128, __nv_bfloat16>(mq, mk, mv, mo, a, st)
                                 : launch_attn_basic<128, __half>(mq, mk, mv, mo, a, st);
