@@ -252,14 +252,14 @@ int kf_attention_fwd(const void* q, const void* kn, const void* v, const void* g
     }
 #endif
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (D == 128 && (variant == 0 || variant == 3)) {
+    if (D == 128 && variant == 3) {
         CUtensorMap mk64, mv64;  // the persistent kernel streams K/V in 64-row tiles
         if (int r = make_map(&mk64, kn, dtype, B, Hkv, S, D, k_sb, k_sh, k_ss, 64)) return r;
         if (int r = make_map(&mv64, v, dtype, B, Hkv, S, D, v_sb, v_sh, v_ss, 64)) return r;
         return dtype == KF_BF16 ? launch_attn_persist<__nv_bfloat16>(mq, mk64, mv64, mo, a, st)
                                 : launch_attn_persist<__half>(mq, mk64, mv64, mo, a, st);
     }
-    if (D == 128 && variant == 2)
+    if (D == 128 && (variant == 0 || variant == 2))
         return dtype == KF_BF16 ? launch_attn_ws<__nv_bfloat16>(mq, mk, mv, mo, a, st)
                                 : launch_attn_ws<__half>(mq, mk, mv, mo, a, st);
     if (variant >= 2) return fail(KF_EINVAL, "the pipelined kernels support head dim 128 only");  // D == 256 here
