@@ -209,7 +209,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     uint64_t* v_empty = bars + 10;  // [stages]
     uint64_t* s_full = bars + 12;   // [tile][buffer] issuer -> softmax group
     uint64_t* p_ready = bars + 16;  // [tile][buffer] softmax group -> issuer (one arrival per warp)
-    uint64_t* pv_done = bars + 20;  // [tile] issuer -> softmax group, one phase per sub-block
+    uint64_t* pv_done = bars + 20;  // [tile][jj & 1] issuer -> softmax group: P V of sub-block jj complete
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 24);
     volatile int* s_abort = reinterpret_cast<volatile int*>(bars + 25);
 
@@ -259,7 +259,8 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             mbar_init(s_full + 2 * i + 1, 1);
             mbar_init(p_ready + 2 * i, 4);
             mbar_init(p_ready + 2 * i + 1, 4);
-            mbar_init(pv_done + i, 1);
+            mbar_init(pv_done + 2 * i, 1);
+            mbar_init(pv_done + 2 * i + 1, 1);
         }
         *s_abort = 0;
         fence_mbar_init();
@@ -304,12 +305,15 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             KF_PE(2);
             float m_used = -INFINITY, den = 0.f;
             const float c = a.scale_log2e;
+            bool s_known_ready = false;
             KF_PROF_DECL;
             for (int jj = 0; jj < tl.nsub && !fail; ++jj) {
                 const int buf = jj & 1;
                 const int n0 = jj * kSub;
                 const uint32_t col_sb = col_s + buf * kSub;
-                if (!mbar_wait_abortable(s_full + 2 * t + buf, (jj >> 1) & 1, s_abort)) { fail = kStatusWsSFull; break; }
+                // (usually already known from the probe issued during the previous sub-block)
+                if (!s_known_ready &&
+                    !mbar_wait_abortable(s_full + 2 * t + buf, (jj >> 1) & 1, s_abort)) { fail = kStatusWsSFull; break; }
                 tc_fence_after();
                 KF_PROF(0);
                 if (jj == 0) KF_PE(3);
@@ -368,16 +372,19 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                     }
                     tmem_st16(lane_base + col_sb + q2 * 16, pk);  // P overwrites its S (already in registers)
                 }
+                // Probe the next score buffer now: the probe is a shared-memory round trip whose latency
+                // overlaps the store completion and barrier traffic below.
+                s_known_ready = (jj + 1 < tl.nsub) &&
+                                mbar_test_wait(s_full + 2 * t + (buf ^ 1), ((jj + 1) >> 1) & 1);
                 float ps0, ps1;
                 f2_unpack(psum, ps0, ps1);
                 den += ps0 + ps1;
                 KF_PROF(3);
-                // Track the completion of the previous P V every sub-block (normally long past):
-                // it keeps this group within one phase of pv_done, and O may only be touched
-                // after it.
-                if (jj > 0 && !mbar_wait_abortable(pv_done + t, (jj - 1) & 1, s_abort)) { fail = kStatusWsPvDone; break; }
                 KF_PROF(4);
                 if (jj > 0 && __any_sync(0xffffffffu, grow)) {
+                    // O may only be touched once the previous P V has completed.  (pv_done alternates
+                    // between two barriers, so a phase cannot be lapped: P V of jj+1 needs this P.)
+                    if (!mbar_wait_abortable(pv_done + 2 * t + ((jj - 1) & 1), ((jj - 1) >> 1) & 1, s_abort)) { fail = kStatusWsPvDone; break; }
                     tc_fence_after();
 #pragma unroll
                     for (int q4 = 0; q4 < D / 32; ++q4) {
@@ -399,7 +406,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             if ((warp & 3) == 0 && lane == 0) KF_PROF_FLUSH(t);
             // ---- epilogue: O / den -> 16-bit -> swizzled smem (this tile's Q buffer) -> TMA store
             KF_PE(7);
-            if (!fail && !mbar_wait_abortable(pv_done + t, (tl.nsub - 1) & 1, s_abort)) fail = kStatusWsODone;
+            if (!fail && !mbar_wait_abortable(pv_done + 2 * t + ((tl.nsub - 1) & 1), ((tl.nsub - 1) >> 1) & 1, s_abort)) fail = kStatusWsODone;
             KF_PE(4);
             if (!fail) {
                 tc_fence_after();
@@ -547,7 +554,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                     tc_fence_after();
                     KF_PROF(3);
                     issue_pv(t, jj);
-                    umma_commit(pv_done + t);
+                    umma_commit(pv_done + 2 * t + (jj & 1));
                     KF_PROF(4);
                 }
                 if ((jj & 1) == 1 || jj == n_sub - 1) umma_commit(v_empty + st0);

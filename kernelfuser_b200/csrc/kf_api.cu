@@ -12,6 +12,7 @@
 #include "attn_fwd_basic.cuh"
 #include "attn_fwd_ws.cuh"
 #include "attn_fwd_persist.cuh"
+#include "attn_fwd_ws2.cuh"
 #include "prepare_rows.cuh"
 
 namespace {
@@ -139,6 +140,23 @@ int launch_attn_ws(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorM
     return KF_OK;
 }
 
+template <typename T>
+int launch_attn_ws2(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
+                   const kf::AttnArgs& a, cudaStream_t st) {
+    auto kern = kf::attn_fwd_ws2_kernel<T>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kf::kWs2SmemBytes);
+    if (e != cudaSuccess) return fail(KF_ECUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
+    const int G = a.Hq / a.Hkv;
+    const long long n_mblk = (a.S + kf::kBM - 1) / kf::kBM;
+    const long long upg = (G % 2 == 0) ? n_mblk * (G / 2) : ((n_mblk + 1) / 2) * G;
+    const long long grid = upg * a.B * a.Hkv;
+    if (grid > 0x7fffffffLL) return fail(KF_EINVAL, "too many tiles");
+    kern<<<(unsigned)grid, kf::kWs2Threads, kf::kWs2SmemBytes, st>>>(mq, mk, mv, mo, a);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(KF_ECUDA, "attention launch failed: %s", cudaGetErrorString(e));
+    return KF_OK;
+}
+
 int sm_count() {
     static int cached[64];
     int dev = 0;
@@ -228,7 +246,7 @@ int kf_attention_fwd(const void* q, const void* kn, const void* v, const void* g
         if (!stride_ok(s)) return fail(KF_EALIGN, "strides must be non-negative multiples of 8 elements");
     if (q_ss < D || k_ss < D || v_ss < D || o_ss < D) return fail(KF_EINVAL, "row stride must be at least D");
     if (!(scale > 0.f) || !(scale < 1e30f)) return fail(KF_EINVAL, "scale must be positive and finite");
-    if (variant < 0 || variant > 3) return fail(KF_EINVAL, "variant must be 0..3");
+    if (variant < 0 || variant > 4) return fail(KF_EINVAL, "variant must be 0..4");
     if (int r = check_device()) return r;
 
     CUtensorMap mq, mk, mv, mo;
@@ -259,6 +277,9 @@ int kf_attention_fwd(const void* q, const void* kn, const void* v, const void* g
         return dtype == KF_BF16 ? launch_attn_persist<__nv_bfloat16>(mq, mk64, mv64, mo, a, st)
                                 : launch_attn_persist<__half>(mq, mk64, mv64, mo, a, st);
     }
+    if (D == 128 && variant == 4)
+        return dtype == KF_BF16 ? launch_attn_ws2<__nv_bfloat16>(mq, mk, mv, mo, a, st)
+                                : launch_attn_ws2<__half>(mq, mk, mv, mo, a, st);
     if (D == 128 && (variant == 0 || variant == 2))
         return dtype == KF_BF16 ? launch_attn_ws<__nv_bfloat16>(mq, mk, mv, mo, a, st)
                                 : launch_attn_ws<__half>(mq, mk, mv, mo, a, st);

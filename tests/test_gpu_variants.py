@@ -10,7 +10,7 @@ from oracle import oracle as orc
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("variant", [1, 2, 3])
+@pytest.mark.parametrize("variant", [1, 2, 3, 4])
 @pytest.mark.parametrize("s,hq,hkv,causal,dtype", [
     (517, 8, 2, True, torch.bfloat16),    # even GQA group: two heads per CTA, ragged tail
     (390, 6, 2, True, torch.float16),     # odd group size: two query blocks of one head per CTA
