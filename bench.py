@@ -301,10 +301,10 @@ def main():
     e2e_steps = max(args.e2e_steps, 1)
 
     def e2e_step():
-        for d, h in zip((dq, dk, dv), host):
-            d.copy_(h, non_blocking=True)
-        op()
-        host_out.copy_(out, non_blocking=True)
+        # public host-buffer API: pinned host q/k/v -> device (chunked over the batch, copies overlapped
+        # with the kernels), operator, output -> pinned host
+        kf.optimized_attention_host(host[0], host[1], host[2], *small, causal=w.causal, eps=w.eps,
+                                    out=host_out, device=dev)
 
     e2e_step()
     barrier()

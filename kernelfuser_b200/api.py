@@ -231,3 +231,84 @@ def optimized_attention_static(q, k, v, gq, gk, cos, sin, out, *, causal=False, 
             float(eps), sc, *_strides3(q), *_strides3(k), *_strides3(v), *_strides3(out),
             st.data_ptr(), stream))
     return out
+
+
+# --------------------------------------------------------------------------
+# Host-buffer entry point: batch-chunked, copy/compute overlapped
+# --------------------------------------------------------------------------
+class _HostPipeline:
+    """Device staging buffers, streams and events for one (device, chunk shape, dtype)."""
+
+    def __init__(self, device, qshape, kshape, dtype):
+        self.key = (device, tuple(qshape), tuple(kshape), dtype)
+        mk = lambda shape: [torch.empty(shape, dtype=dtype, device=device) for _ in range(2)]
+        self.q, self.k, self.v = mk(qshape), mk(kshape), mk(kshape)
+        self.kn, self.o = mk(kshape), mk(qshape)
+        self.h2d = torch.cuda.Stream(device=device)
+        self.d2h = torch.cuda.Stream(device=device)
+        self.compute = torch.cuda.Stream(device=device)
+
+
+_pipelines = {}
+
+
+def optimized_attention_host(q, k, v, gq, gk, cos=None, sin=None, *, causal=False, norm_style="hf",
+                             eps=1e-6, scale=None, out=None, device=None, chunk_batch=None):
+    """``optimized_attention`` for HOST tensors: q/k/v (and the returned output) live in CPU
+    memory, pinned for full copy speed.  The batch is cut into chunks and three streams overlap
+    the host-to-device copy of chunk i+1, the kernels of chunk i and the device-to-host copy of
+    chunk i-1 (PCIe is full duplex), with two sets of device staging buffers that are kept and
+    reused across calls.  Same semantics and errors as ``optimized_attention``; gamma vectors
+    and rotary tables may be CPU or device tensors.  Returns the output as a pinned CPU tensor
+    ([B, Hq, S, D]) after synchronising the copies."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    if q.is_cuda or k.is_cuda or v.is_cuda:
+        raise ValueError("optimized_attention_host takes host tensors; use optimized_attention for device tensors")
+    if q.ndim != 4 or k.ndim != 4 or k.shape != v.shape or q.shape[0] != k.shape[0]:
+        raise ValueError("Expected Q [B,Hq,S,D] and K/V [B,Hkv,S,D]")
+    b = q.shape[0]
+    cb = chunk_batch or max(1, b // 8)
+    q, k, v = (t if t.is_pinned() else t.contiguous().pin_memory() for t in (q, k, v))
+    if out is None:
+        out = torch.empty(q.shape, dtype=q.dtype).pin_memory()
+    small = [None if t is None else t.to(dev, non_blocking=True) for t in (gq, gk, cos, sin)]
+    qshape, kshape = (cb,) + tuple(q.shape[1:]), (cb,) + tuple(k.shape[1:])
+    key = (dev, qshape, kshape, q.dtype)
+    pl = _pipelines.get(key)
+    if pl is None:
+        pl = _pipelines[key] = _HostPipeline(dev, qshape, kshape, q.dtype)
+    cur = torch.cuda.current_stream(dev)
+    for st in (pl.h2d, pl.compute, pl.d2h):
+        st.wait_stream(cur)  # the small tensors above, and any earlier use of the staging buffers
+    n_chunks = (b + cb - 1) // cb
+    ev_comp = [None] * n_chunks
+    ev_d2h = [None] * n_chunks
+    for c in range(n_chunks):
+        lo, hi = c * cb, min((c + 1) * cb, b)
+        n, sl = hi - lo, c & 1
+        with torch.cuda.stream(pl.h2d):
+            if c >= 2:
+                pl.h2d.wait_event(ev_comp[c - 2])  # the kernels that read this buffer set are done
+            pl.q[sl][:n].copy_(q[lo:hi], non_blocking=True)
+            pl.k[sl][:n].copy_(k[lo:hi], non_blocking=True)
+            pl.v[sl][:n].copy_(v[lo:hi], non_blocking=True)
+            ev_in = torch.cuda.Event()
+            ev_in.record(pl.h2d)
+        with torch.cuda.stream(pl.compute):
+            pl.compute.wait_event(ev_in)
+            if c >= 2:
+                pl.compute.wait_event(ev_d2h[c - 2])  # the output buffer has been copied out
+            optimized_attention(pl.q[sl][:n], pl.k[sl][:n], pl.v[sl][:n], *small, causal=causal,
+                                norm_style=norm_style, eps=eps, scale=scale, out=pl.o[sl][:n], kn=pl.kn[sl][:n])
+            ev_comp[c] = torch.cuda.Event()
+            ev_comp[c].record(pl.compute)
+        with torch.cuda.stream(pl.d2h):
+            pl.d2h.wait_event(ev_comp[c])
+            out[lo:hi].copy_(pl.o[sl][:n], non_blocking=True)
+            ev_d2h[c] = torch.cuda.Event()
+            ev_d2h[c].record(pl.d2h)
+    cur.wait_stream(pl.d2h)
+    cur.wait_stream(pl.compute)
+    cur.wait_stream(pl.h2d)
+    cur.synchronize()
+    return out

@@ -166,3 +166,18 @@ def test_cuda_graph_capture_replay():
     torch.cuda.synchronize()
     kf.check_status()
     assert torch.equal(out.view(torch.int16), eager.view(torch.int16))
+
+
+def test_host_buffer_entry_point_matches_device_path():
+    # pinned host tensors in, pinned host tensor out; ragged last chunk (B = 5, chunks of 2)
+    xs = kf.make_inputs(5, 260, 8, 2, 128, seed=17)
+    want = kf.optimized_attention(*to_dev(xs), causal=True)
+    got = kf.optimized_attention_host(*xs, causal=True, chunk_batch=2)
+    again = kf.optimized_attention_host(*xs, causal=True, chunk_batch=2)  # staging buffers are reused
+    torch.cuda.synchronize()
+    kf.check_status()
+    assert got.is_pinned() and not got.is_cuda
+    assert torch.equal(got.view(torch.int16), want.cpu().view(torch.int16))
+    assert torch.equal(again.view(torch.int16), got.view(torch.int16))
+    with pytest.raises(ValueError):
+        kf.optimized_attention_host(*to_dev(xs), causal=True)
