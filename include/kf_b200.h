@@ -66,10 +66,12 @@ int kf_prepare_rows(const void* x, void* y, const void* gamma, const void* cos_t
  * fuse_q = 0: q is already prepared (mode 'unfused').
  * kn is the prepared K from kf_prepare_rows; v is the raw V.
  * scale is the softmax scale (the reference passes D^-0.5).
- * variant: 0 = choose automatically (pipelined kernel for D = 128, baseline
- * kernel for D = 256), 1 = baseline kernel, 2 = pipelined one-item-per-CTA
- * kernel (D = 128), 3 = persistent pipelined kernel (D = 128; measured ~3 %
- * slower than variant 2 on the prefill workloads). */
+ * variant: 0 = choose automatically (the pipelined kernel of the head dim),
+ * 1 = baseline kernel (softmax and MMA serialised inside a CTA; any head dim),
+ * 2 = pipelined, warp-specialised kernel (D = 128: two Q tiles per CTA;
+ * D = 256: one), 3 = persistent pipelined kernel (D = 128), 4 = pipelined
+ * kernel with two softmax warps per 32 rows (D = 128).  3 and 4 are measured
+ * alternatives that are slower than 2 on the prefill workloads. */
 int kf_attention_fwd(const void* q, const void* kn, const void* v, const void* gamma_q,
                      const void* cos_table, const void* sin_table, void* out,
                      int B, int Hq, int Hkv, int S, int D, int dtype,

@@ -13,6 +13,7 @@
 #include "attn_fwd_ws.cuh"
 #include "attn_fwd_persist.cuh"
 #include "attn_fwd_ws2.cuh"
+#include "attn_fwd_ws256.cuh"
 #include "prepare_rows.cuh"
 
 namespace {
@@ -157,6 +158,21 @@ int launch_attn_ws2(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensor
     return KF_OK;
 }
 
+template <typename T>
+int launch_attn_ws256(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
+                      const kf::AttnArgs& a, cudaStream_t st) {
+    auto kern = kf::attn_fwd_ws256_kernel<T>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kf::kW256SmemBytes);
+    if (e != cudaSuccess) return fail(KF_ECUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
+    const long long n_mblk = (a.S + kf::kBM - 1) / kf::kBM;
+    const long long grid = n_mblk * a.B * a.Hq;
+    if (grid > 0x7fffffffLL) return fail(KF_EINVAL, "too many tiles");
+    kern<<<(unsigned)grid, kf::kW256Threads, kf::kW256SmemBytes, st>>>(mq, mk, mv, mo, a);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(KF_ECUDA, "attention launch failed: %s", cudaGetErrorString(e));
+    return KF_OK;
+}
+
 int sm_count() {
     static int cached[64];
     int dev = 0;
@@ -283,7 +299,14 @@ int kf_attention_fwd(const void* q, const void* kn, const void* v, const void* g
     if (D == 128 && (variant == 0 || variant == 2))
         return dtype == KF_BF16 ? launch_attn_ws<__nv_bfloat16>(mq, mk, mv, mo, a, st)
                                 : launch_attn_ws<__half>(mq, mk, mv, mo, a, st);
-    if (variant >= 2) return fail(KF_EINVAL, "the pipelined kernels support head dim 128 only");  // D == 256 here
+    if (D == 256 && (variant == 0 || variant == 2)) {
+        CUtensorMap mk64, mv64;  // K/V stream in 64-row tiles
+        if (int r = make_map(&mk64, kn, dtype, B, Hkv, S, D, k_sb, k_sh, k_ss, 64)) return r;
+        if (int r = make_map(&mv64, v, dtype, B, Hkv, S, D, v_sb, v_sh, v_ss, 64)) return r;
+        return dtype == KF_BF16 ? launch_attn_ws256<__nv_bfloat16>(mq, mk64, mv64, mo, a, st)
+                                : launch_attn_ws256<__half>(mq, mk64, mv64, mo, a, st);
+    }
+    if (variant >= 2) return fail(KF_EINVAL, "variants 3 and 4 support head dim 128 only");  // D == 256 here
     if (D == 128)
         return dtype == KF_BF16 ? launch_attn_basic<128, __nv_bfloat16>(mq, mk, mv, mo, a, st)
                                 : launch_attn_basic<128, __half>(mq, mk, mv, mo, a, st);

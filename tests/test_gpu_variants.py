@@ -39,7 +39,24 @@ def test_many_items_per_persistent_cta():
         assert orc.within_tolerance(orc.metric(o.cpu(), ref))
 
 
-def test_pipelined_variants_reject_d256():
+def test_persistent_and_split_row_variants_reject_d256():
     xs = [x.cuda() for x in kf.make_inputs(1, 64, 2, 1, 256, seed=1)]
-    with pytest.raises(ValueError):
-        kf.optimized_attention(*xs, causal=True, variant=3)
+    for variant in (3, 4):
+        with pytest.raises(ValueError):
+            kf.optimized_attention(*xs, causal=True, variant=variant)
+
+
+@pytest.mark.parametrize("variant", [1, 2])
+@pytest.mark.parametrize("s,hq,hkv,causal,dtype", [
+    (517, 4, 2, True, torch.bfloat16),
+    (200, 3, 1, False, torch.float16),
+    (64, 2, 2, True, torch.bfloat16),
+])
+def test_d256_variants_match_oracle(variant, s, hq, hkv, causal, dtype):
+    xs = kf.make_inputs(2, s, hq, hkv, 256, dtype=dtype, theta=1e4, seed=60 + variant)
+    ref = orc.oracle_fp32(*xs, causal)
+    out = kf.optimized_attention(*[x.cuda() for x in xs], causal=causal, variant=variant)
+    torch.cuda.synchronize()
+    kf.check_status()
+    m = orc.metric(out.cpu(), ref)
+    assert orc.within_tolerance(m), (variant, s, hq, hkv, m)
