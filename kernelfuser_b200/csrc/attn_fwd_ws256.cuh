@@ -4,7 +4,11 @@
 // src/e1_rope_publication_v1.py:609-649; Q prologue :619-623; rounding contract `_rows`
 // :551-582).  At head dim 256 the output accumulator alone takes 256 of the 512 TMEM columns,
 // so a CTA owns ONE 128-row Q tile:
-//   TMEM   : two 64-column score buffers (columns 0..127) | O (columns 128..383)
+//   TMEM   : two 64-column score buffers (columns 0..127) | O (columns 128..383) |
+//            Q as 16-bit pairs (columns 384..511): the prepared Q tile is copied from shared
+//            memory into TMEM once, so Q K^T takes its A operand from TMEM and only K is
+//            streamed from shared memory (an SS MMA with N = 64 re-reads 4 KB of Q per
+//            instruction and is shared-memory bound)
 //   smem   : Q 64 KB, K ring 2 x 32 KB (64 keys x 256), V ring 2 x 32 KB
 //   warps  : 0-3 softmax + Q prologue + epilogue (thread r <-> row r), 4 TMA producer,
 //            5 MMA issuer (one elected lane)
@@ -34,6 +38,7 @@ attn_fwd_ws256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     constexpr int D = 256;
     constexpr uint32_t kTmemCols = 512;
     constexpr uint32_t kColO = 128;
+    constexpr uint32_t kColQ = 384;  // 128 columns: 256 16-bit values per row
     constexpr uint32_t kIdescQK = umma_idesc(Num<T>::kFmt, 0, kBM, kSub);
     constexpr uint32_t kIdescPV = umma_idesc(Num<T>::kFmt, 1, kBM, D);
 
@@ -114,7 +119,23 @@ attn_fwd_ws256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             if (!ok) fail = kStatusWsQFull;
         }
         if (!fail) {
-            fence_proxy_async_smem();
+            // every row of the tile has been transformed by some thread of this group: make that visible,
+            // then thread r copies row r (512 bytes) into TMEM columns [kColQ, kColQ+128)
+            named_barrier_sync(2, 128);
+            const uint8_t* qrow = smem_q + r * 128;
+            const int sw = r & 7;
+#pragma unroll
+            for (int bx = 0; bx < 4; ++bx) {
+                uint32_t w[32];
+#pragma unroll
+                for (int ch = 0; ch < 8; ++ch) {
+                    const uint4 u = *reinterpret_cast<const uint4*>(qrow + bx * kBoxBytes + ((ch ^ sw) << 4));
+                    w[ch * 4 + 0] = u.x; w[ch * 4 + 1] = u.y; w[ch * 4 + 2] = u.z; w[ch * 4 + 3] = u.w;
+                }
+                tmem_st32(lane_base + kColQ + bx * 32, w);
+            }
+            tmem_wait_st();
+            tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(q_ready);
         }
@@ -276,20 +297,20 @@ attn_fwd_ws256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     } else {
         // =================================================== MMA issuer
         if (elect_one()) {
-            const uint32_t q_addr = smem_u32(smem_q), k_addr = smem_u32(smem_k), v_addr = smem_u32(smem_v);
+            const uint32_t k_addr = smem_u32(smem_k), v_addr = smem_u32(smem_v);
             const uint64_t qk_desc = umma_desc_sw128(0, 16, 1024);               // K-major operands (Q and K)
             const uint64_t v_desc = umma_desc_sw128(0, kW256KvBoxBytes, 1024);   // MN-major operand (V)
             const uint32_t qk_hi = static_cast<uint32_t>(qk_desc >> 32), v_hi = static_cast<uint32_t>(v_desc >> 32);
-            const uint32_t q_lo = static_cast<uint32_t>(qk_desc) | ((q_addr & 0x3FFFFu) >> 4);
             const uint32_t k_lo = static_cast<uint32_t>(qk_desc) | ((k_addr & 0x3FFFFu) >> 4);
             const uint32_t v_lo = static_cast<uint32_t>(v_desc) | ((v_addr & 0x3FFFFu) >> 4);
             auto issue_qk = [&](int stage, int buf) {
                 const uint32_t ka = k_lo + stage * (kW256KvTileBytes >> 4);
                 const uint32_t d = tmem_base + buf * kSub;
+                const uint32_t qa = tmem_base + kColQ;
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
-                    umma_ss_lohi(d, q_lo + (ks / 4) * (kBoxBytes >> 4) + (ks % 4) * 2, qk_hi,
-                                 ka + (ks / 4) * (kW256KvBoxBytes >> 4) + (ks % 4) * 2, qk_hi, kIdescQK, ks > 0 ? 1u : 0u);
+                    umma_ts_lohi(d, qa + ks * 8, ka + (ks / 4) * (kW256KvBoxBytes >> 4) + (ks % 4) * 2, qk_hi, kIdescQK,
+                                 ks > 0 ? 1u : 0u);
                 }
             };
             auto issue_pv = [&](int stage, int buf, uint32_t accumulate) {
