@@ -11,9 +11,9 @@
 //   * warps 0-3 / 4-7: softmax + Q prologue + epilogue of tile 0 / tile 1
 //     (thread r <-> row r <-> TMEM lane r);  warp 8: TMA producer (K/V rings of
 //     128-row tiles, raw Q tiles);  warps 9 / 10: MMA issuer of tile 0 / tile 1
-//     (one elected lane each - a tcgen05.mma takes ~45 clocks to issue from one
-//     thread, so one issuer cannot keep the pipe fed with 64-clock MMAs; the two
-//     tiles are independent except for releasing the shared K/V stages);
+//     (one lane each, chosen by elect.sync so that the MMAs issue on the uniform
+//     datapath; the two tiles are independent except for releasing the shared
+//     K/V stages);
 //   * the KV loop advances in SUB-BLOCKS of 64 keys.  TMEM (512 columns) holds,
 //     per tile, two 64-column score buffers and a 128-column output:
 //     S0a S0b | S1a S1b | O0 | O1.  Because scores are double-buffered the issuer

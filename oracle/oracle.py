@@ -14,7 +14,7 @@ container and running its ``oracle_fp32`` on seeded inputs
 Two independent things live here:
 
 1. ``oracle_fp32`` / ``oracle_fp32_explicit`` -- the FP32 oracle every arm of
-   the reference is judged against (src/e1_rope_publication_v1.py:295-302,
+   the reference is checked against (src/e1_rope_publication_v1.py:295-302,
    with helpers ``rope_torch(fp32=True)`` :141-168 and ``expand`` :170).  The
    first form calls ``scaled_dot_product_attention`` exactly as the reference
    does; the second spells the softmax out so the oracle does not depend on
