@@ -66,12 +66,15 @@ int kf_prepare_rows(const void* x, void* y, const void* gamma, const void* cos_t
  * fuse_q = 0: q is already prepared (mode 'unfused').
  * kn is the prepared K from kf_prepare_rows; v is the raw V.
  * scale is the softmax scale (the reference passes D^-0.5).
- * variant: 0 = choose automatically (the pipelined kernel of the head dim),
+ * variant: 0 = choose automatically (D = 256: kernel 2; D = 128: kernel 5 when
+ * B*Hq*ceil(S/128) <= 1024 query tiles, else kernel 2),
  * 1 = baseline kernel (softmax and MMA serialised inside a CTA; any head dim),
  * 2 = pipelined, warp-specialised kernel (D = 128: two Q tiles per CTA;
  * D = 256: one), 3 = persistent pipelined kernel (D = 128), 4 = pipelined
- * kernel with two softmax warps per 32 rows (D = 128).  3 and 4 are measured
- * alternatives that are slower than 2 on the prefill workloads. */
+ * kernel with two softmax warps per 32 rows (D = 128), 5 = the one-tile-per-CTA
+ * pipelined kernel of D = 256 instantiated for D = 128 with two CTAs per SM.
+ * 3 and 4 are measured alternatives that are slower than 2 on the prefill
+ * workloads; 5 is faster than 2 on small problems and slower on large ones. */
 int kf_attention_fwd(const void* q, const void* kn, const void* v, const void* gamma_q,
                      const void* cos_table, const void* sin_table, void* out,
                      int B, int Hq, int Hkv, int S, int D, int dtype,

@@ -24,21 +24,26 @@
 namespace kf {
 
 constexpr int kW256Threads = 192;
-constexpr int kW256QBytes = 4 * kBoxBytes;            // 128 rows x 256 columns
 constexpr int kW256KvBoxBytes = kSub * 128;           // 64 rows x 64 columns
-constexpr int kW256KvTileBytes = 4 * kW256KvBoxBytes; // 64 rows x 256 columns
 constexpr int kW256Stages = 2;
-constexpr int kW256SmemBytes = kW256QBytes + 2 * kW256Stages * kW256KvTileBytes + 1024 + 512;
+template <int D> __host__ __device__ constexpr int ws1_q_bytes() { return (D / 64) * kBoxBytes; }            // 128 rows x D columns
+template <int D> __host__ __device__ constexpr int ws1_kv_tile_bytes() { return (D / 64) * kW256KvBoxBytes; } // 64 rows x D columns
+template <int D> __host__ __device__ constexpr int ws1_smem_bytes() {
+    return ws1_q_bytes<D>() + 2 * kW256Stages * ws1_kv_tile_bytes<D>() + 1024 + 512;
+}
 
-template <typename T>
-__global__ void __launch_bounds__(kW256Threads, 1)
-attn_fwd_ws256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+template <int D, typename T>
+__global__ void __launch_bounds__(kW256Threads, (D == 128 ? 2 : 1))
+attn_fwd_ws1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
                       const AttnArgs a) {
-    constexpr int D = 256;
-    constexpr uint32_t kTmemCols = 512;
+    constexpr int NB = D / 64;                      // 64-column boxes per row
+    constexpr bool kQInTmem = (D == 256);           // room for Q in TMEM only at D = 256 (one CTA per SM)
+    constexpr uint32_t kTmemCols = (D == 256) ? 512 : 256;  // D = 128: two CTAs share the SM's 512 columns
     constexpr uint32_t kColO = 128;
-    constexpr uint32_t kColQ = 384;  // 128 columns: 256 16-bit values per row
+    constexpr uint32_t kColQ = 384;  // D = 256 only: 128 columns = 256 16-bit values per row
+    constexpr int kW256QBytes = ws1_q_bytes<D>();
+    constexpr int kW256KvTileBytes = ws1_kv_tile_bytes<D>();
     constexpr uint32_t kIdescQK = umma_idesc(Num<T>::kFmt, 0, kBM, kSub);
     constexpr uint32_t kIdescPV = umma_idesc(Num<T>::kFmt, 1, kBM, D);
 
@@ -119,20 +124,24 @@ attn_fwd_ws256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             if (!ok) fail = kStatusWsQFull;
         }
         if (!fail) {
-            // every row of the tile has been transformed by some thread of this group: make that visible,
-            // then thread r copies row r (512 bytes) into TMEM columns [kColQ, kColQ+128)
-            named_barrier_sync(2, 128);
-            const uint8_t* qrow = smem_q + r * 128;
-            const int sw = r & 7;
+            if constexpr (kQInTmem) {
+                // every row of the tile has been transformed by some thread of this group: make that
+                // visible, then thread r copies row r into TMEM columns [kColQ, kColQ + D/2)
+                named_barrier_sync(2, 128);
+                const uint8_t* qrow = smem_q + r * 128;
+                const int sw = r & 7;
 #pragma unroll
-            for (int bx = 0; bx < 4; ++bx) {
-                uint32_t w[32];
+                for (int bx = 0; bx < NB; ++bx) {
+                    uint32_t w[32];
 #pragma unroll
-                for (int ch = 0; ch < 8; ++ch) {
-                    const uint4 u = *reinterpret_cast<const uint4*>(qrow + bx * kBoxBytes + ((ch ^ sw) << 4));
-                    w[ch * 4 + 0] = u.x; w[ch * 4 + 1] = u.y; w[ch * 4 + 2] = u.z; w[ch * 4 + 3] = u.w;
+                    for (int ch = 0; ch < 8; ++ch) {
+                        const uint4 u = *reinterpret_cast<const uint4*>(qrow + bx * kBoxBytes + ((ch ^ sw) << 4));
+                        w[ch * 4 + 0] = u.x; w[ch * 4 + 1] = u.y; w[ch * 4 + 2] = u.z; w[ch * 4 + 3] = u.w;
+                    }
+                    tmem_st32(lane_base + kColQ + bx * 32, w);
                 }
-                tmem_st32(lane_base + kColQ + bx * 32, w);
+            } else {
+                fence_proxy_async_smem();  // Q stays in shared memory as the A operand
             }
             tmem_wait_st();
             tc_fence_before();
@@ -262,7 +271,7 @@ attn_fwd_ws256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         named_barrier_sync(1, 128);
         if (warp == 0 && elect_one() && *s_abort == 0) {
 #pragma unroll
-            for (int bx = 0; bx < 4; ++bx) tma_store_4d(&tm_o, smem_q + bx * kBoxBytes, bx * 64, m0, h, b);
+            for (int bx = 0; bx < NB; ++bx) tma_store_4d(&tm_o, smem_q + bx * kBoxBytes, bx * 64, m0, h, b);
             tma_store_commit();
             tma_store_wait_read();  // the buffer must outlive the copy's reads; the writes drain on their own
         }
@@ -271,7 +280,7 @@ attn_fwd_ws256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         if (elect_one()) {
             mbar_expect_tx(q_full, kW256QBytes);
 #pragma unroll
-            for (int bx = 0; bx < 4; ++bx) tma_load_4d(smem_q + bx * kBoxBytes, &tm_q, q_full, bx * 64, m0, h, b);
+            for (int bx = 0; bx < NB; ++bx) tma_load_4d(smem_q + bx * kBoxBytes, &tm_q, q_full, bx * 64, m0, h, b);
             q_issued = 1;
             int s = 0;
             uint32_t epar = 1;  // passes at once on the first turn of the ring
@@ -279,12 +288,12 @@ attn_fwd_ws256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 if (!mbar_wait_abortable(k_empty + s, epar, s_abort)) { fail = kStatusWsKEmpty; break; }
                 mbar_expect_tx(k_full + s, kW256KvTileBytes);
 #pragma unroll
-                for (int bx = 0; bx < 4; ++bx)
+                for (int bx = 0; bx < NB; ++bx)
                     tma_load_4d(smem_k + s * kW256KvTileBytes + bx * kW256KvBoxBytes, &tm_k, k_full + s, bx * 64, jj * kSub, kh, b);
                 if (!mbar_wait_abortable(v_empty + s, epar, s_abort)) { fail = kStatusWsVEmpty; break; }
                 mbar_expect_tx(v_full + s, kW256KvTileBytes);
 #pragma unroll
-                for (int bx = 0; bx < 4; ++bx)
+                for (int bx = 0; bx < NB; ++bx)
                     tma_load_4d(smem_v + s * kW256KvTileBytes + bx * kW256KvBoxBytes, &tm_v, v_full + s, bx * 64, jj * kSub, kh, b);
                 kv_issued = jj + 1;
                 if (++s == kW256Stages) { s = 0; epar ^= 1; }
@@ -303,14 +312,19 @@ attn_fwd_ws256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             const uint32_t qk_hi = static_cast<uint32_t>(qk_desc >> 32), v_hi = static_cast<uint32_t>(v_desc >> 32);
             const uint32_t k_lo = static_cast<uint32_t>(qk_desc) | ((k_addr & 0x3FFFFu) >> 4);
             const uint32_t v_lo = static_cast<uint32_t>(v_desc) | ((v_addr & 0x3FFFFu) >> 4);
+            const uint32_t q_lo = static_cast<uint32_t>(qk_desc) | ((smem_u32(smem_q) & 0x3FFFFu) >> 4);
             auto issue_qk = [&](int stage, int buf) {
                 const uint32_t ka = k_lo + stage * (kW256KvTileBytes >> 4);
                 const uint32_t d = tmem_base + buf * kSub;
-                const uint32_t qa = tmem_base + kColQ;
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
-                    umma_ts_lohi(d, qa + ks * 8, ka + (ks / 4) * (kW256KvBoxBytes >> 4) + (ks % 4) * 2, qk_hi, kIdescQK,
-                                 ks > 0 ? 1u : 0u);
+                    const uint32_t kb = ka + (ks / 4) * (kW256KvBoxBytes >> 4) + (ks % 4) * 2;
+                    if constexpr (kQInTmem) {
+                        umma_ts_lohi(d, tmem_base + kColQ + ks * 8, kb, qk_hi, kIdescQK, ks > 0 ? 1u : 0u);
+                    } else {
+                        umma_ss_lohi(d, q_lo + (ks / 4) * (kBoxBytes >> 4) + (ks % 4) * 2, qk_hi, kb, qk_hi, kIdescQK,
+                                     ks > 0 ? 1u : 0u);
+                    }
                 }
             };
             auto issue_pv = [&](int stage, int buf, uint32_t accumulate) {

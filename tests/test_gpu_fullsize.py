@@ -4,7 +4,8 @@ C5: B=8, S=8192, Hq=16, Hkv=8, D=256) checked through size-independent propertie
 * sampled rows against the FP32 oracle evaluated for exactly those rows (cheap: one query row
   costs S*D work), including the first row, tile boundaries and the last row;
 * a causal first row attends to one key, so it must equal V's first row bit for bit;
-* batch independence: one batch element computed alone is bit-identical to the full call;
+* batch independence: one batch element computed alone by the same kernel is bit-identical to the
+  full call;
 * the whole output is finite and fully written (it starts as NaN).
 """
 import pytest
@@ -57,7 +58,10 @@ def test_full_size_properties(name):
         assert orc.within_tolerance(m), (name, b, h, m)
     # batch independence, bit for bit
     b = w.B // 2
-    alone = kf.optimized_attention(dx[0][b:b + 1], dx[1][b:b + 1], dx[2][b:b + 1], *dx[3:], causal=True)
+    # (variant 2 is what the automatic choice ran for the full call; a single batch element is small
+    # enough for the automatic choice to pick another kernel, whose rounding differs in the last bit)
+    alone = kf.optimized_attention(dx[0][b:b + 1], dx[1][b:b + 1], dx[2][b:b + 1], *dx[3:], causal=True,
+                                   variant=2)
     torch.cuda.synchronize()
     kf.check_status()
     assert torch.equal(alone.view(torch.int16), out[b:b + 1].view(torch.int16))

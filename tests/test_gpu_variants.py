@@ -1,4 +1,4 @@
-"""Every attention kernel variant (baseline, pipelined, persistent) against the
+"""Every attention kernel variant (baseline, pipelined, persistent, one tile per CTA) against the
 FP32 oracle on the same inputs; the default (automatic) choice is covered by
 tests/test_gpu_attention.py."""
 import pytest
@@ -10,7 +10,7 @@ from oracle import oracle as orc
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("variant", [1, 2, 3, 4])
+@pytest.mark.parametrize("variant", [1, 2, 3, 4, 5])
 @pytest.mark.parametrize("s,hq,hkv,causal,dtype", [
     (517, 8, 2, True, torch.bfloat16),    # even GQA group: two heads per CTA, ragged tail
     (390, 6, 2, True, torch.float16),     # odd group size: two query blocks of one head per CTA
@@ -18,7 +18,9 @@ pytestmark = pytest.mark.gpu
     (64, 4, 4, True, torch.bfloat16),     # a single sub-block
 ])
 def test_variant_matches_oracle(variant, s, hq, hkv, causal, dtype):
-    xs = kf.make_inputs(3, s, hq, hkv, 128, dtype=dtype, seed=40 + variant)
+    # one seed for all variants: every kernel sees the same rows, so a difference
+    # between variants is a difference between kernels, not between inputs
+    xs = kf.make_inputs(3, s, hq, hkv, 128, dtype=dtype, seed=41)
     ref = orc.oracle_fp32(*xs, causal)
     out = kf.optimized_attention(*[x.cuda() for x in xs], causal=causal, variant=variant)
     torch.cuda.synchronize()
@@ -41,7 +43,7 @@ def test_many_items_per_persistent_cta():
 
 def test_persistent_and_split_row_variants_reject_d256():
     xs = [x.cuda() for x in kf.make_inputs(1, 64, 2, 1, 256, seed=1)]
-    for variant in (3, 4):
+    for variant in (3, 4, 5):
         with pytest.raises(ValueError):
             kf.optimized_attention(*xs, causal=True, variant=variant)
 
@@ -53,7 +55,7 @@ def test_persistent_and_split_row_variants_reject_d256():
     (64, 2, 2, True, torch.bfloat16),
 ])
 def test_d256_variants_match_oracle(variant, s, hq, hkv, causal, dtype):
-    xs = kf.make_inputs(2, s, hq, hkv, 256, dtype=dtype, theta=1e4, seed=60 + variant)
+    xs = kf.make_inputs(2, s, hq, hkv, 256, dtype=dtype, theta=1e4, seed=61)
     ref = orc.oracle_fp32(*xs, causal)
     out = kf.optimized_attention(*[x.cuda() for x in xs], causal=causal, variant=variant)
     torch.cuda.synchronize()
