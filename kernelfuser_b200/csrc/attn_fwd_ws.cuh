@@ -264,6 +264,16 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         }
         *s_abort = 0;
         fence_mbar_init();
+        // The raw Q tiles are requested at once: their trip from DRAM then overlaps the TMEM allocation
+        // and the block-wide barrier below instead of following them.
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+            if (tile[t].nsub > 0) {
+                mbar_expect_tx(q_full + t, kWsTileBytes);
+                tma_load_4d(smem_q + t * kWsTileBytes, &tm_q, q_full + t, 0, tile[t].m0, tile[t].h, b);
+                tma_load_4d(smem_q + t * kWsTileBytes + kBoxBytes, &tm_q, q_full + t, 64, tile[t].m0, tile[t].h, b);
+            }
+        }
     }
     if (warp == 0) {
         __syncwarp();
@@ -277,7 +287,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 
     int fail = 0;
     // producer bookkeeping for the exit path (lane 0 of warp 8)
-    int k_issued = 0, v_issued = 0, q_issued[2] = {0, 0};
+    int k_issued = 0, v_issued = 0;
 
     if (warp < 8) {
         // =================================================== softmax group t
@@ -452,15 +462,6 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     } else if (warp == 8) {
         // =================================================== TMA producer
         if (elect_one()) {
-#pragma unroll
-            for (int t = 0; t < 2; ++t) {
-                if (tile[t].nsub > 0) {
-                    mbar_expect_tx(q_full + t, kWsTileBytes);
-                    tma_load_4d(smem_q + t * kWsTileBytes, &tm_q, q_full + t, 0, tile[t].m0, tile[t].h, b);
-                    tma_load_4d(smem_q + t * kWsTileBytes + kBoxBytes, &tm_q, q_full + t, 64, tile[t].m0, tile[t].h, b);
-                    q_issued[t] = 1;
-                }
-            }
             for (int j = 0; j < n_loop && !fail; ++j) {
                 const int s = j % kWsStages, u = j / kWsStages;
                 if (u > 0 && !mbar_wait_abortable(k_empty + s, (u - 1) & 1, s_abort)) { fail = kStatusWsKEmpty; break; }
@@ -576,7 +577,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         // leave no copy in flight into this CTA's shared memory
 #pragma unroll
         for (int t = 0; t < 2; ++t)
-            if (q_issued[t]) mbar_wait(q_full + t, 0);
+            if (tile[t].nsub > 0) mbar_wait(q_full + t, 0);
 #pragma unroll
         for (int s = 0; s < kWsStages; ++s) {
             // last load issued into stage s (if any)

@@ -99,6 +99,11 @@ attn_fwd_ws1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         }
         *s_abort = 0;
         fence_mbar_init();
+        // The raw Q tile is requested at once: its trip from DRAM then overlaps the TMEM allocation and
+        // the block-wide barrier below instead of following them.
+        mbar_expect_tx(q_full, kW256QBytes);
+#pragma unroll
+        for (int bx = 0; bx < NB; ++bx) tma_load_4d(smem_q + bx * kBoxBytes, &tm_q, q_full, bx * 64, m0, h, b);
     }
     if (warp == 0) {
         __syncwarp();
@@ -111,7 +116,7 @@ attn_fwd_ws1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const uint32_t tmem_base = *tmem_slot;
 
     int fail = 0;
-    int kv_issued = 0, q_issued = 0;  // producer bookkeeping for the exit path
+    int kv_issued = 0;  // producer bookkeeping for the exit path
 
     if (warp < 4) {
         // =================================================== softmax, Q prologue, epilogue
@@ -278,10 +283,6 @@ attn_fwd_ws1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     } else if (warp == 4) {
         // =================================================== TMA producer
         if (elect_one()) {
-            mbar_expect_tx(q_full, kW256QBytes);
-#pragma unroll
-            for (int bx = 0; bx < NB; ++bx) tma_load_4d(smem_q + bx * kBoxBytes, &tm_q, q_full, bx * 64, m0, h, b);
-            q_issued = 1;
             int s = 0;
             uint32_t epar = 1;  // passes at once on the first turn of the ring
             for (int jj = 0; jj < n_sub; ++jj) {
@@ -370,7 +371,7 @@ attn_fwd_ws1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     __syncthreads();
     if (warp == 4 && *s_abort != 0 && elect_one()) {
         // leave no copy in flight into this CTA's shared memory
-        if (q_issued) mbar_wait(q_full, 0);
+        mbar_wait(q_full, 0);
 #pragma unroll
         for (int s = 0; s < kW256Stages; ++s) {
             if (kv_issued > s) {
