@@ -176,13 +176,22 @@ def optimized_attention(q, k, v, gq, gk, cos=None, sin=None, *, causal=False,
     return out
 
 
-def fused(q, k, v, gq, gk, cos, sin, causal, eps=1e-6, scale=None, norm_style="qwen3"):
+def fused(q, k, v, gq, gk, cos, sin, causal, eps=1e-6, scale=None, norm_style="qwen3", *, out_layout="bhsd"):
     """Runner-arm adapter with the signature of the reference's arms
     (``fused``/``separate``/``vendor``/``compiled_fn``,
     src/e1_rope_publication_v1.py:185-225).  Accepts [S,D], [B,S,D] or
     [B,1,S,D] tables (the first broadcast slice is used, :192-200), an
     explicit ``scale``/``eps``, and head-transposed (non-contiguous) q/k/v
-    views as produced by a model's ``view(...).transpose(1, 2)``."""
+    views as produced by a model's ``view(...).transpose(1, 2)``, so the
+    projections' [B,S,H,D] outputs are read in place.
+
+    ``out_layout='bshd'`` (keyword-only extension) makes the kernel write the
+    result where the model's output projection wants it: the returned tensor
+    is contiguous [B, S, Hq*D], i.e. the ``transpose(1, 2).reshape(B, S, -1)``
+    that follows the attention call in a decoder layer
+    (src/e2_qwen3_rope_prefill.py:159) costs no copy."""
+    if out_layout not in ("bhsd", "bshd"):
+        raise ValueError("out_layout must be 'bhsd' or 'bshd'")
     if cos is not None:
         if cos.ndim == 4: cos = cos[:, 0]
         if sin.ndim == 4: sin = sin[:, 0]
@@ -195,13 +204,18 @@ def fused(q, k, v, gq, gk, cos, sin, causal, eps=1e-6, scale=None, norm_style="q
     for t in (q, k, v):
         if t.stride(3) != 1 or any(st % 8 for st in t.stride()[:3]):
             raise ValueError("q/k/v need a contiguous head dimension and 16-byte aligned strides")
-    out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    b, hq, s, d = q.shape
+    if out_layout == "bshd":
+        flat = torch.empty((b, s, hq * d), dtype=q.dtype, device=q.device)
+        out = flat.view(b, s, hq, d).transpose(1, 2)  # [B,Hq,S,D] view with row stride Hq*D
+    else:
+        flat = out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
     kn = torch.empty(k.shape, dtype=k.dtype, device=k.device)
     with torch.cuda.device(q.device):
         prepare_rows(k, gk.contiguous(), cos, sin, norm_style=style, eps=eps, out=kn)
         attention_forward(q, kn, v, gq.contiguous(), cos, sin, out, causal=causal, norm_style=style,
                           fuse_q=True, eps=eps, scale=scale)
-    return out
+    return flat
 
 
 def optimized_attention_static(q, k, v, gq, gk, cos, sin, out, *, causal=False, norm_style="hf",

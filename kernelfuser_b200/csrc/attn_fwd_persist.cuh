@@ -102,7 +102,7 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     uint64_t* v_empty = bars + 15;   // [stage]  2 arrivals
     uint64_t* s_full = bars + 18;    // [tile][buffer]
     uint64_t* p_ready = bars + 22;   // [tile][buffer] 4 arrivals (one per softmax warp)
-    uint64_t* pv_done = bars + 26;   // [tile] one phase per sub-block
+    uint64_t* pv_done = bars + 26;   // [tile][g & 1] issuer -> softmax group: P V of this tile's g-th sub-block complete
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 32);
     volatile int* s_abort = reinterpret_cast<volatile int*>(bars + 33);
 
@@ -122,7 +122,8 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
             mbar_init(s_full + 2 * i + 1, 1);
             mbar_init(p_ready + 2 * i, 4);
             mbar_init(p_ready + 2 * i + 1, 4);
-            mbar_init(pv_done + i, 1);
+            mbar_init(pv_done + 2 * i, 1);
+            mbar_init(pv_done + 2 * i + 1, 1);
         }
 #pragma unroll
         for (int i = 0; i < kPsKvStages; ++i) {
@@ -183,12 +184,15 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
             float m_used = -INFINITY, den = 0.f;
             PolyBase pb;
             pb.set(0.f, inv_c);
+            bool s_known_ready = false;
             for (int jj = 0; jj < my_nsub; ++jj) {
                 const int gg = g + jj;
                 const int buf = gg & 1;
                 const int n0 = jj * kSub;
                 const uint32_t col_sb = col_s + buf * kSub;
-                if (!mbar_wait_abortable(s_full + 2 * t + buf, (gg >> 1) & 1, s_abort)) { fail = kStatusPsSFull; break; }
+                // (usually already known from the probe issued during the previous sub-block)
+                if (!s_known_ready &&
+                    !mbar_wait_abortable(s_full + 2 * t + buf, (gg >> 1) & 1, s_abort)) { fail = kStatusPsSFull; break; }
                 tc_fence_after();
                 KF_PROF(0);
                 if ((warp & 3) == 1 && lane == 0) KF_TL(t, n, jj, 0);
@@ -250,18 +254,22 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                     }
                     tmem_st16(lane_base + col_sb + q2 * 16, pk);  // P overwrites its S (already in registers)
                 }
+                // Probe the next score buffer now: the probe is a shared-memory round trip whose latency
+                // overlaps the store completion and barrier traffic below.
+                s_known_ready = (jj + 1 < my_nsub) &&
+                                mbar_test_wait(s_full + 2 * t + (buf ^ 1), ((gg + 1) >> 1) & 1);
                 float ps0, ps1;
                 f2_unpack(psum, ps0, ps1);
                 den += ps0 + ps1;
                 KF_PROF(3);
                 if ((warp & 3) == 1 && lane == 0) KF_TL(t, n, jj, 2);
-                // Track the completion of the previous P V every sub-block (normally long past): it keeps
-                // this group within one phase of pv_done, and O may only be touched after it.  (At jj == 0
-                // the epilogue of the previous item has already observed the last P V.)
-                if (jj > 0 && !mbar_wait_abortable(pv_done + t, (gg - 1) & 1, s_abort)) { fail = kStatusPsPvDone; break; }
                 KF_PROF(4);
                 if ((warp & 3) == 1 && lane == 0) KF_TL(t, n, jj, 3);
                 if (jj > 0 && __any_sync(0xffffffffu, grow)) {
+                    // O may only be touched once the previous P V has completed.  (pv_done alternates
+                    // between two barriers, so a phase cannot be lapped: the scores of sub-block g were
+                    // written after P V of g-2, the tensor pipe runs in order, and P V of g+1 needs this P.)
+                    if (!mbar_wait_abortable(pv_done + 2 * t + ((gg - 1) & 1), ((gg - 1) >> 1) & 1, s_abort)) { fail = kStatusPsPvDone; break; }
                     tc_fence_after();
 #pragma unroll
                     for (int q4 = 0; q4 < D / 32; ++q4) {
@@ -283,7 +291,7 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
             if (fail) break;
             g += my_nsub;
             // ---- epilogue: O / den -> 16-bit -> swizzled smem (this tile's Q slot) -> TMA store
-            if (!mbar_wait_abortable(pv_done + t, (g - 1) & 1, s_abort)) { fail = kStatusPsPvDone; break; }
+            if (!mbar_wait_abortable(pv_done + 2 * t + ((g - 1) & 1), ((g - 1) >> 1) & 1, s_abort)) { fail = kStatusPsPvDone; break; }
             tc_fence_after();
             {
                 const float inv_den = 1.f / den;
@@ -439,7 +447,7 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                         KF_PROF(4);
                         KF_TL(2 + t, n, jj, 2);
                         issue_pv(vst, np & 1, jj > 0 ? 1u : 0u);
-                        umma_commit(pv_done + t);
+                        umma_commit(pv_done + 2 * t + (np & 1));
                         ++np;
                     }
                     umma_commit(v_empty + vst);

@@ -126,6 +126,25 @@ def test_arm_adapter_accepts_model_style_views():
     check(out.cpu(), ref, "arm adapter")
 
 
+def test_arm_adapter_writes_the_projection_layout():
+    # [B,S,H,D] projections in, [B,S,Hq*D] out: no layout copy on either side of the operator
+    b, s, hq, hkv, d = 2, 333, 8, 2, 128
+    q, k, v, gq, gk, cos, sin = kf.make_inputs(b, s, hq, hkv, d, seed=23)
+    ref = orc.oracle_fp32(q, k, v, gq, gk, cos, sin, True)
+    views = [t.transpose(1, 2).contiguous().to(DEV).transpose(1, 2) for t in (q, k, v)]
+    small = to_dev([gq, gk, cos, sin])
+    flat = kf.fused(*views, *small, True, out_layout="bshd")
+    plain = kf.fused(*views, *small, True)
+    torch.cuda.synchronize()
+    kf.check_status()
+    assert flat.shape == (b, s, hq * d) and flat.is_contiguous()
+    as_bhsd = flat.view(b, s, hq, d).transpose(1, 2)
+    check(as_bhsd.contiguous().cpu(), ref, "bshd output")
+    assert torch.equal(as_bhsd.contiguous().view(torch.int16), plain.view(torch.int16))
+    with pytest.raises(ValueError):
+        kf.fused(*views, *small, True, out_layout="sbhd")
+
+
 def test_output_fully_written_and_deterministic():
     xs = to_dev(kf.make_inputs(2, 333, 8, 2, 128, seed=8))
     out1 = torch.full_like(xs[0], float("nan"))
