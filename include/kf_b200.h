@@ -85,6 +85,25 @@ int kf_attention_fwd(const void* q, const void* kn, const void* v, const void* g
                      int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s,
                      int* status, int variant, void* stream);
 
+/* Factored no-RoPE form of the operator, both launches in one call.  Replaces
+ * `launch_factored_attention` (src/e1_qk_publication_v3.py:638-650:
+ * `prepare_factored_kernel` :593-611 + `factored_attention_kernel` :614-635).
+ * kn (caller's scratch, shape of k) receives r(k * inv_rms(k) * gamma_k * gamma_q)
+ * (one rounding); the RAW q feeds Q K^T and each query row's scores are scaled by
+ * inv_rms(q_row) * scale * log2(e).  The reference keeps inv_rms(q) in a separate
+ * FP32 tensor [B,Hq,S]; here it is computed in the attention prologue and stays on
+ * chip, so there is no such argument.  No rotary tables in this form.  Opt-in: its
+ * rounding points differ from kf_prepare_rows + kf_attention_fwd. */
+int kf_factored_attention(const void* q, const void* k, const void* v, const void* gamma_q, const void* gamma_k,
+                          void* kn, void* out, int B, int Hq, int Hkv, int S, int D, int dtype, int causal,
+                          float eps, float scale,
+                          int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
+                          int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_s,
+                          int64_t v_stride_b, int64_t v_stride_h, int64_t v_stride_s,
+                          int64_t kn_stride_b, int64_t kn_stride_h, int64_t kn_stride_s,
+                          int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s,
+                          int* status, void* stream);
+
 /* Whole operator without any allocation (no counterpart in the reference,
  * whose wrapper always allocates its prepared-K scratch with torch.empty_like).
  * For callers that cannot allocate device memory where they call from: hosts

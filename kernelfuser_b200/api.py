@@ -218,6 +218,39 @@ def fused(q, k, v, gq, gk, cos, sin, causal, eps=1e-6, scale=None, norm_style="q
     return flat
 
 
+def factored_attention(q, k, v, gq, gk, *, causal=False, eps=1e-6, scale=None, out=None, kn=None):
+    """No-RoPE attention in the reference's FACTORED form (``launch_factored_attention``,
+    src/e1_qk_publication_v3.py:638-650): the query weight is folded into the prepared keys,
+    ``KN = r(k * inv_rms(k) * gk * gq)``, the raw ``q`` feeds Q K^T and every query row's scores
+    are scaled by ``inv_rms(q_row) * scale * log2(e)``.  Mathematically the same operator as
+    ``optimized_attention`` without tables, with fewer roundings on the Q side and no rounded
+    Q at all; opt-in because the rounding points differ.  The reference's FP32 ``INV``
+    tensor does not exist here: the inverse RMS is computed in the attention prologue."""
+    lib = _lib.load()
+    gq, gk = gq.contiguous(), gk.contiguous()
+    _validate(q, k, v, gq, gk, None, None, "query", 128, "legacy", require_contiguous=False)
+    if not (eps > 0):
+        raise ValueError("eps must be positive")
+    for t in (q, k, v):  # head-transposed views of [B,S,H,D] projections are read in place
+        if t.stride(3) != 1 or any(st % 8 for st in t.stride()[:3]):
+            raise ValueError("q/k/v need a contiguous head dimension and 16-byte aligned strides")
+    out = torch.empty(q.shape, dtype=q.dtype, device=q.device) if out is None else out
+    kn = torch.empty(k.shape, dtype=k.dtype, device=k.device) if kn is None else kn
+    if out.shape != q.shape or out.dtype != q.dtype or kn.shape != k.shape or kn.dtype != k.dtype:
+        raise ValueError("out / kn must match q / k in shape and dtype")
+    b, hq, s, d = q.shape
+    sc = float(d ** -0.5 if scale is None else scale)
+    with torch.cuda.device(q.device):
+        st = status_word(q.device)
+        stream = torch.cuda.current_stream().cuda_stream
+        _call(lib.kf_factored_attention(
+            _ptr(q), _ptr(k), _ptr(v), _ptr(gq), _ptr(gk), _ptr(kn), _ptr(out),
+            b, hq, k.shape[1], s, d, _DTYPES[q.dtype], int(bool(causal)), float(eps), sc,
+            *_strides3(q), *_strides3(k), *_strides3(v), *_strides3(kn), *_strides3(out),
+            st.data_ptr(), stream))
+    return out
+
+
 def optimized_attention_static(q, k, v, gq, gk, cos, sin, out, *, causal=False, norm_style="hf",
                                eps=1e-6, scale=None):
     """The whole operator through ``kf_optimized_attention_static``: the

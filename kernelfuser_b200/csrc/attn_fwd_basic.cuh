@@ -36,6 +36,7 @@ struct AttnArgs {
     float scale_log2e;  // softmax scale * log2(e)
     float eps;
     int causal, rope, hf_norm, fuse_q;
+    int factored;  // factored no-RoPE form: q stays raw, scores are scaled by the row's inverse RMS
     int* status;  // device status word: 0 = ok, else first failure code
 #ifdef KF_PROFILE
     long long* prof;  // per-role cycle counters of one CTA (profiling builds only)
@@ -118,6 +119,37 @@ __device__ __forceinline__ bool q_prologue_coop(uint8_t* smem_q, int gtid, int m
             *plo = lo;
             *phi = hi;
         }
+    }
+    return true;
+}
+
+// Factored no-RoPE form (the reference's `factored_attention_kernel`,
+// src/e1_qk_publication_v3.py:614-635): the query weight has been folded into the prepared keys, so
+// the Q tile stays raw and only inv[r] = rsqrt(sum_j q[r,j]^2 / D + eps) is needed, which multiplies
+// the row's softmax scale.  Same cooperative mapping as q_prologue_coop (D/16 lanes per row); the lane
+// holding the row's first chunk stores the result.  The caller synchronises the 128 threads before
+// reading inv_out.  Returns false if the wait failed.
+template <int D, typename T, typename WaitFn>
+__device__ __forceinline__ bool q_inv_coop(const uint8_t* smem_q, int gtid, const AttnArgs& a, float* inv_out,
+                                           WaitFn&& wait_q) {
+    constexpr int LPR = D / 16;
+    constexpr int RPW = 32 / LPR;
+    constexpr int NIT = kBM / (4 * RPW);
+    constexpr int NB = D / 64;
+    const int lane = gtid & 31, w = gtid >> 5;
+    const int sub = lane % LPR, rsub = lane / LPR;
+    if (!wait_q()) return false;
+#pragma unroll
+    for (int it = 0; it < NIT; ++it) {
+        const int r = it * 4 * RPW + w * RPW + rsub;
+        const uint8_t* row = smem_q + r * 128;
+        const int off = ((sub % 8) ^ (r & 7)) << 4;
+        const uint4 lo = *reinterpret_cast<const uint4*>(row + (sub / 8) * kBoxBytes + off);
+        const uint4 hi = *reinterpret_cast<const uint4*>(row + (sub / 8 + NB / 2) * kBoxBytes + off);
+        float ss = sumsq_chunk<T>(hi, sumsq_chunk<T>(lo, 0.f));
+#pragma unroll
+        for (int m = LPR / 2; m >= 1; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
+        if (sub == 0) inv_out[r] = rsqrtf(ss * (1.0f / static_cast<float>(D)) + a.eps);
     }
     return true;
 }

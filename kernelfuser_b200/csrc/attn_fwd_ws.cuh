@@ -44,7 +44,7 @@ enum : int {
 constexpr int kWsThreads = 352;  // 8 softmax warps, 1 producer warp, 2 issuer warps
 constexpr int kWsStages = 2;
 constexpr int kWsTileBytes = 2 * kBoxBytes;  // 128 rows x 128 columns of 16-bit values
-constexpr int kWsSmemBytes = (2 + 2 * kWsStages) * kWsTileBytes + 1024 + 512;
+constexpr int kWsSmemBytes = (2 + 2 * kWsStages) * kWsTileBytes + 1024 + 512 + 1024;  // tiles, alignment, barriers, inverse RMS of the Q rows
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 constexpr int kSub = 64;                    // keys per sub-block
 
@@ -212,6 +212,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     uint64_t* pv_done = bars + 20;  // [tile][jj & 1] issuer -> softmax group: P V of sub-block jj complete
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 24);
     volatile int* s_abort = reinterpret_cast<volatile int*>(bars + 25);
+    float* s_inv = reinterpret_cast<float*>(bars + 64);  // [tile][row] inverse RMS of the raw Q rows (factored form)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -303,7 +304,8 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             KF_PE(0);
             {
                 auto wait_q = [&]() { return mbar_wait_abortable(q_full + t, 0, s_abort); };
-                const bool ok = a.fuse_q ? q_prologue_coop<D, T>(my_q, r, tl.m0, a, wait_q) : wait_q();
+                const bool ok = a.factored ? q_inv_coop<D, T>(my_q, r, a, s_inv + t * kBM, wait_q)
+                                : a.fuse_q ? q_prologue_coop<D, T>(my_q, r, tl.m0, a, wait_q) : wait_q();
                 if (!ok) fail = kStatusWsQFull;
             }
             KF_PE(1);
@@ -314,7 +316,11 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             }
             KF_PE(2);
             float m_used = -INFINITY, den = 0.f;
-            const float c = a.scale_log2e;
+            float c = a.scale_log2e;
+            if (a.factored && !fail) {  // (a failed wait fails in every thread of the group alike)
+                named_barrier_sync(1 + t, 128);
+                c *= s_inv[t * kBM + r];
+            }
             bool s_known_ready = false;
             KF_PROF_DECL;
             for (int jj = 0; jj < tl.nsub && !fail; ++jj) {

@@ -29,7 +29,7 @@ constexpr int kW256Stages = 2;
 template <int D> __host__ __device__ constexpr int ws1_q_bytes() { return (D / 64) * kBoxBytes; }            // 128 rows x D columns
 template <int D> __host__ __device__ constexpr int ws1_kv_tile_bytes() { return (D / 64) * kW256KvBoxBytes; } // 64 rows x D columns
 template <int D> __host__ __device__ constexpr int ws1_smem_bytes() {
-    return ws1_q_bytes<D>() + 2 * kW256Stages * ws1_kv_tile_bytes<D>() + 1024 + 512;
+    return ws1_q_bytes<D>() + 2 * kW256Stages * ws1_kv_tile_bytes<D>() + 1024 + 512 + 512;  // tiles, alignment, barriers, inverse RMS of the Q rows
 }
 
 template <int D, typename T>
@@ -66,6 +66,7 @@ attn_fwd_ws1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     uint64_t* pv_done = bars + 14;  // [jj & 1]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
     volatile int* s_abort = reinterpret_cast<volatile int*>(bars + 17);
+    float* s_inv = reinterpret_cast<float*>(bars + 64);  // [row] inverse RMS of the raw Q rows (factored form)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -125,8 +126,14 @@ attn_fwd_ws1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         const int row = m0 + r;
         {
             auto wait_q = [&]() { return mbar_wait_abortable(q_full, 0, s_abort); };
-            const bool ok = a.fuse_q ? q_prologue_coop<D, T, 4>(smem_q, r, m0, a, wait_q) : wait_q();
+            const bool ok = a.factored ? q_inv_coop<D, T>(smem_q, r, a, s_inv, wait_q)
+                            : a.fuse_q ? q_prologue_coop<D, T, 4>(smem_q, r, m0, a, wait_q) : wait_q();
             if (!ok) fail = kStatusWsQFull;
+        }
+        float c = a.scale_log2e;
+        if (a.factored && !fail) {  // (a failed wait fails in every thread of the group alike)
+            named_barrier_sync(3, 128);
+            c *= s_inv[r];
         }
         if (!fail) {
             if constexpr (kQInTmem) {
@@ -154,7 +161,6 @@ attn_fwd_ws1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             if (lane == 0) mbar_arrive(q_ready);
         }
         float m_used = -INFINITY, den = 0.f;
-        const float c = a.scale_log2e;
         const float inv_c = 1.f / c;
         PolyBase pb;
         pb.set(0.f, inv_c);

@@ -89,7 +89,7 @@ int check_common(int B, int H, int S, int D, int dtype) {
     return KF_OK;
 }
 
-template <int D, typename T> int launch_prepare(const kf::PrepareArgs& a, cudaStream_t st) {
+template <int D, typename T, bool FACTORED = false> int launch_prepare(const kf::PrepareArgs& a, cudaStream_t st) {
     constexpr int RPB = (32 / (D / 16)) * (kf::kPrepThreads / 32);
     const int gx = (a.S + RPB - 1) / RPB;
     kf::PrepareArgs args = a;
@@ -102,7 +102,7 @@ template <int D, typename T> int launch_prepare(const kf::PrepareArgs& a, cudaSt
     gy = (BH + per - 1) / per;
     if (gy > 65535) return fail(KF_EINVAL, "too many (batch, head) pairs");
     args.bh_per_cta = per;
-    kf::prepare_rows_kernel<D, T><<<dim3(gx, gy), kf::kPrepThreads, 0, st>>>(args);
+    kf::prepare_rows_kernel<D, T, FACTORED><<<dim3(gx, gy), kf::kPrepThreads, 0, st>>>(args);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(KF_ECUDA, "prepare_rows launch failed: %s", cudaGetErrorString(e));
     return KF_OK;
@@ -218,17 +218,16 @@ extern "C" int kf_prof_read(long long* host_out) {
 }
 #endif
 
-extern "C" {
+namespace {
 
-int kf_version(void) { return 100; }
-
-const char* kf_last_error(void) { return g_err; }
-
-int kf_prepare_rows(const void* x, void* y, const void* gamma, const void* cos_table, const void* sin_table, int B,
+int prepare_impl(const void* x, void* y, const void* gamma, const void* gamma2, const void* cos_table,
+                 const void* sin_table, int B,
                     int H, int S, int D, int dtype, int hf_norm, float eps, int64_t x_sb, int64_t x_sh, int64_t x_ss,
                     int64_t y_sb, int64_t y_sh, int64_t y_ss, void* stream) {
     if (int r = check_common(B, H, S, D, dtype)) return r;
     if (!x || !y || !gamma) return fail(KF_EINVAL, "x, y and gamma must not be NULL");
+    if (gamma2 && (cos_table || sin_table)) return fail(KF_EINVAL, "the factored form has no rotary tables");
+    if (!aligned16(gamma2)) return fail(KF_EALIGN, "pointers must be 16-byte aligned");
     if ((cos_table == nullptr) != (sin_table == nullptr))
         return fail(KF_EINVAL, "provide both rotary tables or neither");
     if (!aligned16(x) || !aligned16(y) || !aligned16(gamma) || !aligned16(cos_table) || !aligned16(sin_table))
@@ -239,19 +238,25 @@ int kf_prepare_rows(const void* x, void* y, const void* gamma, const void* cos_t
     if (x_ss < D || y_ss < D) return fail(KF_EINVAL, "row stride must be at least D");
     if (int r = check_device()) return r;
     kf::PrepareArgs a{};
-    a.x = x; a.y = y; a.gamma = gamma; a.cos = cos_table; a.sin = sin_table;
+    a.x = x; a.y = y; a.gamma = gamma; a.gamma2 = gamma2; a.cos = cos_table; a.sin = sin_table;
     a.x_sb = x_sb; a.x_sh = x_sh; a.x_ss = x_ss; a.y_sb = y_sb; a.y_sh = y_sh; a.y_ss = y_ss;
     a.B = B; a.H = H; a.S = S; a.eps = eps; a.rope = cos_table != nullptr; a.hf_norm = hf_norm != 0;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (gamma2) {
+        if (D == 128)
+            return dtype == KF_BF16 ? launch_prepare<128, __nv_bfloat16, true>(a, st)
+                                    : launch_prepare<128, __half, true>(a, st);
+        return dtype == KF_BF16 ? launch_prepare<256, __nv_bfloat16, true>(a, st) : launch_prepare<256, __half, true>(a, st);
+    }
     if (D == 128) return dtype == KF_BF16 ? launch_prepare<128, __nv_bfloat16>(a, st) : launch_prepare<128, __half>(a, st);
     return dtype == KF_BF16 ? launch_prepare<256, __nv_bfloat16>(a, st) : launch_prepare<256, __half>(a, st);
 }
 
-int kf_attention_fwd(const void* q, const void* kn, const void* v, const void* gamma_q, const void* cos_table,
+int attention_impl(const void* q, const void* kn, const void* v, const void* gamma_q, const void* cos_table,
                      const void* sin_table, void* out, int B, int Hq, int Hkv, int S, int D, int dtype, int causal,
                      int hf_norm, int fuse_q, float eps, float scale, int64_t q_sb, int64_t q_sh, int64_t q_ss,
                      int64_t k_sb, int64_t k_sh, int64_t k_ss, int64_t v_sb, int64_t v_sh, int64_t v_ss,
-                     int64_t o_sb, int64_t o_sh, int64_t o_ss, int* status, int variant, void* stream) {
+                     int64_t o_sb, int64_t o_sh, int64_t o_ss, int* status, int variant, int factored, void* stream) {
     if (int r = check_common(B, Hq, S, D, dtype)) return r;
     if (Hkv < 1 || Hq % Hkv != 0) return fail(KF_EINVAL, "Hq (%d) must be a positive multiple of Hkv (%d)", Hq, Hkv);
     if (!q || !kn || !v || !out || !status) return fail(KF_EINVAL, "q, kn, v, out and status must not be NULL");
@@ -281,6 +286,10 @@ int kf_attention_fwd(const void* q, const void* kn, const void* v, const void* g
     a.scale_log2e = scale * 1.4426950408889634f;
     a.eps = eps; a.causal = causal != 0; a.rope = cos_table != nullptr; a.hf_norm = hf_norm != 0;
     a.fuse_q = fuse_q != 0; a.status = status;
+    a.factored = factored != 0;
+    if (factored && (cos_table || sin_table)) return fail(KF_EINVAL, "the factored form has no rotary tables");
+    if (factored && variant != 0 && variant != 2 && variant != 5)
+        return fail(KF_EINVAL, "the factored form runs on kernels 0, 2 and 5 only");
 #ifdef KF_PROFILE
     {
         void* pp = nullptr;
@@ -330,6 +339,49 @@ int kf_attention_fwd(const void* q, const void* kn, const void* v, const void* g
                                 : launch_attn_basic<128, __half>(mq, mk, mv, mo, a, st);
     return dtype == KF_BF16 ? launch_attn_basic<256, __nv_bfloat16>(mq, mk, mv, mo, a, st)
                             : launch_attn_basic<256, __half>(mq, mk, mv, mo, a, st);
+}
+
+}  // namespace
+
+extern "C" {
+
+int kf_version(void) { return 100; }
+
+const char* kf_last_error(void) { return g_err; }
+
+int kf_prepare_rows(const void* x, void* y, const void* gamma, const void* cos_table, const void* sin_table, int B,
+                    int H, int S, int D, int dtype, int hf_norm, float eps, int64_t x_sb, int64_t x_sh, int64_t x_ss,
+                    int64_t y_sb, int64_t y_sh, int64_t y_ss, void* stream) {
+    return prepare_impl(x, y, gamma, nullptr, cos_table, sin_table, B, H, S, D, dtype, hf_norm, eps, x_sb, x_sh, x_ss,
+                        y_sb, y_sh, y_ss, stream);
+}
+
+int kf_attention_fwd(const void* q, const void* kn, const void* v, const void* gamma_q, const void* cos_table,
+                     const void* sin_table, void* out, int B, int Hq, int Hkv, int S, int D, int dtype, int causal,
+                     int hf_norm, int fuse_q, float eps, float scale, int64_t q_sb, int64_t q_sh, int64_t q_ss,
+                     int64_t k_sb, int64_t k_sh, int64_t k_ss, int64_t v_sb, int64_t v_sh, int64_t v_ss,
+                     int64_t o_sb, int64_t o_sh, int64_t o_ss, int* status, int variant, void* stream) {
+    return attention_impl(q, kn, v, gamma_q, cos_table, sin_table, out, B, Hq, Hkv, S, D, dtype, causal, hf_norm,
+                          fuse_q, eps, scale, q_sb, q_sh, q_ss, k_sb, k_sh, k_ss, v_sb, v_sh, v_ss, o_sb, o_sh, o_ss,
+                          status, variant, /*factored=*/0, stream);
+}
+
+// Factored no-RoPE form of the operator (the reference's `launch_factored_attention`,
+// src/e1_qk_publication_v3.py:638-650): KN = r(k * inv_k * gamma_k * gamma_q) is written to `kn`, the raw
+// query feeds the score product and each row's scores are scaled by its inverse RMS, which stays on chip
+// (the reference stores it in a separate FP32 tensor).
+int kf_factored_attention(const void* q, const void* k, const void* v, const void* gamma_q, const void* gamma_k,
+                          void* kn, void* out, int B, int Hq, int Hkv, int S, int D, int dtype, int causal, float eps,
+                          float scale, int64_t q_sb, int64_t q_sh, int64_t q_ss, int64_t k_sb, int64_t k_sh,
+                          int64_t k_ss, int64_t v_sb, int64_t v_sh, int64_t v_ss, int64_t n_sb, int64_t n_sh,
+                          int64_t n_ss, int64_t o_sb, int64_t o_sh, int64_t o_ss, int* status, void* stream) {
+    if (!gamma_q || !gamma_k) return fail(KF_EINVAL, "gamma_q and gamma_k must not be NULL");
+    if (int r = prepare_impl(k, kn, gamma_k, gamma_q, nullptr, nullptr, B, Hkv, S, D, dtype, /*hf_norm=*/0, eps, k_sb,
+                             k_sh, k_ss, n_sb, n_sh, n_ss, stream))
+        return r;
+    return attention_impl(q, kn, v, gamma_q, nullptr, nullptr, out, B, Hq, Hkv, S, D, dtype, causal, /*hf_norm=*/0,
+                          /*fuse_q=*/1, eps, scale, q_sb, q_sh, q_ss, n_sb, n_sh, n_ss, v_sb, v_sh, v_ss, o_sb, o_sh,
+                          o_ss, status, /*variant=*/0, /*factored=*/1, stream);
 }
 
 }  // extern "C"

@@ -25,6 +25,7 @@ struct PrepareArgs {
     const void* x;
     void* y;
     const void* gamma;  // [D]
+    const void* gamma2; // [D] second weight vector of the factored no-RoPE form, else null
     const void* cos;    // [S, D] or null
     const void* sin;    // [S, D] or null
     long long x_sb, x_sh, x_ss;  // element strides of x (batch, head, row); D is contiguous
@@ -44,7 +45,10 @@ struct PrepareArgs {
 constexpr int kPrepThreads = 256;
 constexpr int kPrepUnroll = KF_PREP_UNROLL;  // rows in flight per lane
 
-template <int D, typename T>
+// FACTORED: y = r(x * inv * gamma * gamma2), one rounding, no rotation - the K side of the reference's
+// factored no-RoPE form (`prepare_factored_kernel`, src/e1_qk_publication_v3.py:593-611), which folds the
+// query weight into the prepared keys so that the query itself needs only its inverse RMS.
+template <int D, typename T, bool FACTORED = false>
 __global__ void __launch_bounds__(kPrepThreads, KF_PREP_MINBLK) prepare_rows_kernel(const PrepareArgs a) {
     constexpr int LPR = D / 16;                      // lanes per row
     constexpr int RPW = 32 / LPR;                    // rows per warp
@@ -58,7 +62,11 @@ __global__ void __launch_bounds__(kPrepThreads, KF_PREP_MINBLK) prepare_rows_ker
     const uint4* g4 = reinterpret_cast<const uint4*>(a.gamma);
     const uint4 glo = __ldg(g4 + sub), ghi = __ldg(g4 + LPR + sub);
     uint4 clo = make_uint4(0, 0, 0, 0), chi = clo, slo = clo, shi = clo;
-    if (rope && valid) {
+    if constexpr (FACTORED) {  // the table registers carry the second weight vector instead
+        const uint4* h4 = reinterpret_cast<const uint4*>(a.gamma2);
+        clo = __ldg(h4 + sub);
+        chi = __ldg(h4 + LPR + sub);
+    } else if (rope && valid) {
         const uint4* c4 = reinterpret_cast<const uint4*>(a.cos) + static_cast<long long>(pos) * (D / 8);
         const uint4* s4 = reinterpret_cast<const uint4*>(a.sin) + static_cast<long long>(pos) * (D / 8);
         clo = __ldg(c4 + sub);
@@ -95,7 +103,12 @@ __global__ void __launch_bounds__(kPrepThreads, KF_PREP_MINBLK) prepare_rows_ker
 #pragma unroll
             for (int m = LPR / 2; m >= 1; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
             const float inv = rsqrtf(ss * (1.0f / static_cast<float>(D)) + a.eps);
-            transform_pair<T>(lo[u], hi[u], inv, glo, ghi, clo, chi, slo, shi, hf, rope);
+            if constexpr (FACTORED) {
+                scale_chunk2<T>(lo[u], inv, glo, clo);
+                scale_chunk2<T>(hi[u], inv, ghi, chi);
+            } else {
+                transform_pair<T>(lo[u], hi[u], inv, glo, ghi, clo, chi, slo, shi, hf, rope);
+            }
             if (valid && p < bh1) {
                 const int b = p / a.H, h = p - b * a.H;
                 uint4* dst = reinterpret_cast<uint4*>(yb + b * a.y_sb + h * a.y_sh + pos * a.y_ss);

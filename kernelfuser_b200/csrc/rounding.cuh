@@ -103,6 +103,21 @@ template <typename T> __device__ __forceinline__ uint32_t norm2(uint32_t x, floa
     return Num<T>::pack(__fmul_rn(__fmul_rn(f.x, inv), gf.x), __fmul_rn(__fmul_rn(f.y, inv), gf.y));
 }
 
+// r(((x * inv) * g) * g2) for the 8 values of a chunk: the fp32 product chain of the reference's factored
+// K-prepare (src/e1_qk_publication_v3.py:609), rounded once.
+template <typename T>
+__device__ __forceinline__ void scale_chunk2(uint4& x, float inv, const uint4& g, const uint4& g2) {
+    uint32_t* w = reinterpret_cast<uint32_t*>(&x);
+    const uint32_t* a = reinterpret_cast<const uint32_t*>(&g);
+    const uint32_t* b = reinterpret_cast<const uint32_t*>(&g2);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = Num<T>::unpack(w[i]), ga = Num<T>::unpack(a[i]), gb = Num<T>::unpack(b[i]);
+        w[i] = Num<T>::pack(__fmul_rn(__fmul_rn(__fmul_rn(f.x, inv), ga.x), gb.x),
+                            __fmul_rn(__fmul_rn(__fmul_rn(f.y, inv), ga.y), gb.y));
+    }
+}
+
 // Transform the chunk pair (lo: columns j..j+7 < D/2, hi: columns j+D/2..) in
 // place.  g*/c*/s* are the gamma and table chunks at the same columns.
 template <typename T>

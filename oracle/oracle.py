@@ -26,6 +26,9 @@ Two independent things live here:
    kernels cannot run without a GPU, so this emulation is the stand-in used
    to bound "no worse than the reference's compiled arm".
 
+``emulate_factored_attention`` does the same for the factored no-RoPE form
+(src/e1_qk_publication_v3.py:593-650).
+
 ``metric`` restates the reference's acceptance gate
 (src/e1_rope_publication_v1.py:287-293) and adds the max-abs / mean-abs
 figures the build's tolerance is quoted in.
@@ -145,11 +148,14 @@ def emulate_rows(x, gamma, cos=None, sin=None, *, hf_norm=True, eps=EPS):
     return y.to(dt)
 
 
-def emulate_attention(qn, kn, v, causal=False, scale=None, bm=64, bn=128):
+def emulate_attention(qn, kn, v, causal=False, scale=None, bm=64, bn=128, row_scale=None):
     """Blocked exp2 online softmax of ``attention_v2_kernel``
     (src/e1_rope_publication_v1.py:624-648): fp32 scores from 16-bit
     operands, probabilities rounded to the input dtype for the PV product,
-    unrounded fp32 probabilities in the denominator, fp32 accumulation."""
+    unrounded fp32 probabilities in the denominator, fp32 accumulation.
+    ``row_scale`` [B,H,S] multiplies each query row's score scale (the
+    ``temperature`` of ``factored_attention_kernel``,
+    src/e1_qk_publication_v3.py:621)."""
     dt = qn.dtype
     b, h, s, d = qn.shape
     hk = kn.shape[1]
@@ -169,7 +175,8 @@ def emulate_attention(qn, kn, v, causal=False, scale=None, bm=64, bn=128):
             n1 = min(n0 + bn, s)
             k_t = expand(kf[:, :, n0:n1], h) if g > 1 else kf[:, :, n0:n1]
             v_t = expand(vf[:, :, n0:n1], h) if g > 1 else vf[:, :, n0:n1]
-            z = torch.matmul(q_t, k_t.transpose(-1, -2)) * sc
+            z = torch.matmul(q_t, k_t.transpose(-1, -2))
+            z = z * sc if row_scale is None else z * (row_scale[:, :, m0:m1, None] * sc)
             if causal:
                 ni = torch.arange(n0, n1)
                 z = z.masked_fill(mi[:, None] < ni[None, :], float("-inf"))
@@ -192,6 +199,22 @@ def emulate_optimized_attention(q, k, v, gq, gk, cos=None, sin=None, *, causal=F
     kn = emulate_rows(k, gk, cos, sin, hf_norm=hf, eps=eps)
     qn = emulate_rows(q, gq, cos, sin, hf_norm=hf, eps=eps)
     return emulate_attention(qn, kn, v, causal=causal, scale=scale, bm=64, bn=bn)
+
+
+def emulate_factored_attention(q, k, v, gq, gk, *, causal=False, scale=None, eps=EPS, bn=64):
+    """CPU stand-in for the reference's factored no-RoPE launch
+    (``launch_factored_attention``, src/e1_qk_publication_v3.py:638-650):
+    ``prepare_factored_kernel`` (:593-611) writes ``INV = rsqrt(sum(q^2)/D + eps)``
+    in fp32 and ``KN = r(((k*inv_k)*gk)*gq)`` with one rounding;
+    ``factored_attention_kernel`` (:614-635) multiplies the RAW q with KN and
+    scales each row's scores by ``INV * D^-0.5 * log2(e)``."""
+    dt = q.dtype
+    d = q.shape[-1]
+    qf, kf = q.float(), k.float()
+    inv_q = torch.rsqrt(qf.square().sum(-1) / d + eps)                          # [B,Hq,S] fp32
+    inv_k = torch.rsqrt(kf.square().sum(-1, keepdim=True) / d + eps)
+    kn = (kf * inv_k * gk.float() * gq.float()).to(dt)
+    return emulate_attention(q, kn, v, causal=causal, scale=scale, bm=64, bn=bn, row_scale=inv_q)
 
 
 # --------------------------------------------------------------------------

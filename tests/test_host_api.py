@@ -95,6 +95,11 @@ def test_misuse_raises_value_error():
         kf.optimized_attention(q, k, v, gq, gk, positions=torch.arange(33))
     with pytest.raises(ValueError, match="positions"):
         kf.optimized_attention(q, k, v, gq, gk, cos, sin, positions=torch.arange(33), theta=1e6)
+    # the factored form: CPU tensors, mismatched scratch
+    with pytest.raises(ValueError, match="CUDA"):
+        kf.factored_attention(q, k, v, gq, gk, causal=True)
+    with pytest.raises(ValueError, match="Expected Q"):
+        kf.factored_attention(q, k[:, :, :5], v, gq, gk)
     # the arm adapter: unknown output layout, and CPU tensors
     with pytest.raises(ValueError, match="out_layout"):
         kf.fused(q, k, v, gq, gk, cos, sin, True, out_layout="sbhd")

@@ -23,6 +23,16 @@ def test_oracle_matches_reference_golden(name, causal):
         assert torch.allclose(got, want, atol=2e-5, rtol=1e-5), (name, fn.__name__, (got - want).abs().max())
 
 
+@pytest.mark.parametrize("causal", [False, True])
+def test_factored_emulation_against_the_reference_golden(causal):
+    # the factored no-RoPE form is the same operator as the no-RoPE oracle the reference stored;
+    # its CPU emulation must meet the tolerance the kernels are held to
+    meta, t = load_golden("norope_s33_d128_bf16")
+    want = t["out_causal" if causal else "out_full"]
+    got = orc.emulate_factored_attention(t["q"], t["k"], t["v"], t["gq"], t["gk"], causal=causal)
+    assert orc.within_tolerance(orc.metric(got, want))
+
+
 def test_golden_inputs_regenerate_from_seed():
     # the stored inputs are what the seeded generator produces today
     for name in SMALL_GOLDEN:
