@@ -24,7 +24,10 @@
 //     the TMEM A operand; V is an MN-major shared-memory B operand;
 //   * the running output is rescaled only when a row's maximum grew by more
 //     than 2^8 since the exponent base was last moved (exact after the final
-//     division), and only then does softmax wait for the previous P V;
+//     division), and only then does softmax wait for the previous P V.  Because
+//     that is rare, the probabilities are computed straight from the current
+//     base with the row maximum taken alongside, and a sub-block is redone with
+//     a moved base only when some row of the warp outgrew the threshold;
 //   * CTAs are ordered (batch, KV head) major, heaviest query block first, so
 //     CTAs resident together stream the same K/V through L2.  No cluster
 //     multicast anywhere.
@@ -169,7 +172,14 @@ __device__ __forceinline__ void exp2_poly2_scaled(float s0, float s1, f32x2 c2, 
 }
 
 // Which pairs of a 32-pair sub-block row go through the polynomial (the rest use MUFU ex2).
-constexpr uint32_t kPolyPairMask = 0x88888888u;  // every 4th pair: 25 %
+#ifndef KF_POLY_MASK
+#define KF_POLY_MASK 0x88888888u  // every 4th pair: 25 %
+#endif
+constexpr uint32_t kPolyPairMask = KF_POLY_MASK;
+
+template <bool B> struct BoolTag {
+    static constexpr bool value = B;
+};
 
 struct WsTile {
     int h, m0, nsub;
@@ -348,45 +358,62 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                             if (n >= a.S || (a.causal && n > row)) sr[q2][i] = 0xff800000u;  // -inf
                         }
                 }
-                float mx0 = -INFINITY, mx1 = -INFINITY;
-#pragma unroll
-                for (int q2 = 0; q2 < 2; ++q2)
-#pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        mx0 = max3(mx0, __uint_as_float(sr[q2][i]), __uint_as_float(sr[q2][i + 1]));
-                        mx1 = max3(mx1, __uint_as_float(sr[q2][i + 2]), __uint_as_float(sr[q2][i + 3]));
-                    }
-                const float m_blk = fmaxf(mx0, mx1) * c;
-                // move the exponent base only when the maximum grew by more than the threshold
-                const bool grow = m_blk > m_used + kRescaleThreshold;
-                float alpha = 1.f;
-                if (grow) {
-                    alpha = fast_exp2(m_used - m_blk);  // 0 on the first sub-block
-                    m_used = m_blk;
-                    den *= alpha;
-                }
-                const float neg_m = -m_used;
-                const f32x2 c2 = f2_pack(c, c), nm2 = f2_pack(neg_m, neg_m);
-                f32x2 psum = f2_pack(0.f, 0.f);
+                // The exponent base moves only when a row's maximum has grown by more than the threshold
+                // since it was last moved, which after the first sub-blocks is rare.  So the probabilities
+                // are computed at once from the current base while the row maximum is taken alongside (the
+                // 3-input max instructions fill issue slots the exponentials leave free); only if some row
+                // of the warp did outgrow the threshold is the sub-block redone the exact way: maximum
+                // first, base moved, probabilities again (the scores are still in registers).
+                const f32x2 c2 = f2_pack(c, c);
+                f32x2 psum;
+                float mx0, mx1;
                 KF_PROF(2);
+                auto exp_pass = [&](auto track_max) {
+                    constexpr bool kTrack = decltype(track_max)::value;
+                    const float neg_m = -m_used;
+                    const f32x2 nm2 = f2_pack(neg_m, neg_m);
+                    psum = f2_pack(0.f, 0.f);
+                    mx0 = -INFINITY;
+                    mx1 = -INFINITY;
 #pragma unroll
-                for (int q2 = 0; q2 < 2; ++q2) {
-                    uint32_t pk[16];
+                    for (int q2 = 0; q2 < 2; ++q2) {
+                        uint32_t pk[16];
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        float x0, x1, p0, p1;
-                        f2_unpack(f2_fma(f2_pack(__uint_as_float(sr[q2][2 * i]), __uint_as_float(sr[q2][2 * i + 1])), c2, nm2),
-                                  x0, x1);
-                        if ((kPolyPairMask >> (q2 * 16 + i)) & 1u) {
-                            exp2_poly2(x0, x1, p0, p1);
-                        } else {
-                            p0 = fast_exp2(x0);
-                            p1 = fast_exp2(x1);
+                        for (int i = 0; i < 16; ++i) {
+                            const float s0 = __uint_as_float(sr[q2][2 * i]), s1 = __uint_as_float(sr[q2][2 * i + 1]);
+                            float x0, x1, p0, p1;
+                            f2_unpack(f2_fma(f2_pack(s0, s1), c2, nm2), x0, x1);
+                            if ((kPolyPairMask >> (q2 * 16 + i)) & 1u) {
+                                exp2_poly2(x0, x1, p0, p1);
+                            } else {
+                                p0 = fast_exp2(x0);
+                                p1 = fast_exp2(x1);
+                            }
+                            if constexpr (kTrack) {
+                                if (i & 1) mx1 = max3(mx1, s0, s1);
+                                else mx0 = max3(mx0, s0, s1);
+                            }
+                            psum = f2_add(psum, f2_pack(p0, p1));
+                            pk[i] = Num<T>::pack(p0, p1);
                         }
-                        psum = f2_add(psum, f2_pack(p0, p1));
-                        pk[i] = Num<T>::pack(p0, p1);
+                        tmem_st16(lane_base + col_sb + q2 * 16, pk);  // P overwrites its S (already in registers)
                     }
-                    tmem_st16(lane_base + col_sb + q2 * 16, pk);  // P overwrites its S (already in registers)
+                };
+                bool grow = false;
+                float alpha = 1.f;
+                exp_pass(BoolTag<true>{});
+                {
+                    const float m_blk = fmaxf(mx0, mx1) * c;
+                    if (__any_sync(0xffffffffu, !(m_blk <= m_used + kRescaleThreshold))) {
+                        // ---- the exact way (always taken on a tile's first sub-block)
+                        grow = m_blk > m_used + kRescaleThreshold;
+                        if (grow) {
+                            alpha = fast_exp2(m_used - m_blk);  // 0 on the first sub-block
+                            m_used = m_blk;
+                            den *= alpha;
+                        }
+                        exp_pass(BoolTag<false>{});
+                    }
                 }
                 // Probe the next score buffer now: the probe is a shared-memory round trip whose latency
                 // overlaps the store completion and barrier traffic below.
