@@ -24,10 +24,7 @@
 //     the TMEM A operand; V is an MN-major shared-memory B operand;
 //   * the running output is rescaled only when a row's maximum grew by more
 //     than 2^8 since the exponent base was last moved (exact after the final
-//     division), and only then does softmax wait for the previous P V.  Because
-//     that is rare, the probabilities are computed straight from the current
-//     base with the row maximum taken alongside, and a sub-block is redone with
-//     a moved base only when some row of the warp outgrew the threshold;
+//     division), and only then does softmax wait for the previous P V;
 //   * CTAs are ordered (batch, KV head) major, heaviest query block first, so
 //     CTAs resident together stream the same K/V through L2.  No cluster
 //     multicast anywhere.
@@ -47,7 +44,8 @@ enum : int {
 constexpr int kWsThreads = 352;  // 8 softmax warps, 1 producer warp, 2 issuer warps
 constexpr int kWsStages = 2;
 constexpr int kWsTileBytes = 2 * kBoxBytes;  // 128 rows x 128 columns of 16-bit values
-constexpr int kWsSmemBytes = (2 + 2 * kWsStages) * kWsTileBytes + 1024 + 512 + 1024;  // tiles, alignment, barriers, inverse RMS of the Q rows
+constexpr int kWsSmemBytes = (2 + 2 * kWsStages) * kWsTileBytes + 1024 + 512;  // tiles, alignment slack, barriers
+constexpr int kWsSmemBytesFactored = kWsSmemBytes + 1024;  // + inverse RMS of the Q rows (factored form only)
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 constexpr int kSub = 64;                    // keys per sub-block
 
@@ -177,15 +175,13 @@ __device__ __forceinline__ void exp2_poly2_scaled(float s0, float s1, f32x2 c2, 
 #endif
 constexpr uint32_t kPolyPairMask = KF_POLY_MASK;
 
-template <bool B> struct BoolTag {
-    static constexpr bool value = B;
-};
-
 struct WsTile {
     int h, m0, nsub;
 };
 
-template <typename T>
+// FACTORED selects the factored no-RoPE form (raw Q, per-row inverse RMS folded into the softmax scale); it is a
+// template parameter so that the standard instantiation carries none of it.
+template <typename T, bool FACTORED = false>
 __global__ void __launch_bounds__(kWsThreads, 1)
 attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
@@ -222,7 +218,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     uint64_t* pv_done = bars + 20;  // [tile][jj & 1] issuer -> softmax group: P V of sub-block jj complete
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 24);
     volatile int* s_abort = reinterpret_cast<volatile int*>(bars + 25);
-    float* s_inv = reinterpret_cast<float*>(bars + 64);  // [tile][row] inverse RMS of the raw Q rows (factored form)
+    [[maybe_unused]] float* s_inv = reinterpret_cast<float*>(bars + 64);  // [tile][row] inverse RMS of the raw Q rows (factored form)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -314,8 +310,9 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             KF_PE(0);
             {
                 auto wait_q = [&]() { return mbar_wait_abortable(q_full + t, 0, s_abort); };
-                const bool ok = a.factored ? q_inv_coop<D, T>(my_q, r, a, s_inv + t * kBM, wait_q)
-                                : a.fuse_q ? q_prologue_coop<D, T>(my_q, r, tl.m0, a, wait_q) : wait_q();
+                bool ok;
+                if constexpr (FACTORED) ok = q_inv_coop<D, T>(my_q, r, a, s_inv + t * kBM, wait_q);
+                else ok = a.fuse_q ? q_prologue_coop<D, T>(my_q, r, tl.m0, a, wait_q) : wait_q();
                 if (!ok) fail = kStatusWsQFull;
             }
             KF_PE(1);
@@ -326,11 +323,14 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             }
             KF_PE(2);
             float m_used = -INFINITY, den = 0.f;
-            float c = a.scale_log2e;
-            if (a.factored && !fail) {  // (a failed wait fails in every thread of the group alike)
-                named_barrier_sync(1 + t, 128);
-                c *= s_inv[t * kBM + r];
+            float c_row = a.scale_log2e;
+            if constexpr (FACTORED) {
+                if (!fail) {  // (a failed wait fails in every thread of the group alike)
+                    named_barrier_sync(1 + t, 128);
+                    c_row *= s_inv[t * kBM + r];
+                }
             }
+            const float c = c_row;
             bool s_known_ready = false;
             KF_PROF_DECL;
             for (int jj = 0; jj < tl.nsub && !fail; ++jj) {
@@ -358,62 +358,45 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                             if (n >= a.S || (a.causal && n > row)) sr[q2][i] = 0xff800000u;  // -inf
                         }
                 }
-                // The exponent base moves only when a row's maximum has grown by more than the threshold
-                // since it was last moved, which after the first sub-blocks is rare.  So the probabilities
-                // are computed at once from the current base while the row maximum is taken alongside (the
-                // 3-input max instructions fill issue slots the exponentials leave free); only if some row
-                // of the warp did outgrow the threshold is the sub-block redone the exact way: maximum
-                // first, base moved, probabilities again (the scores are still in registers).
-                const f32x2 c2 = f2_pack(c, c);
-                f32x2 psum;
-                float mx0, mx1;
-                KF_PROF(2);
-                auto exp_pass = [&](auto track_max) {
-                    constexpr bool kTrack = decltype(track_max)::value;
-                    const float neg_m = -m_used;
-                    const f32x2 nm2 = f2_pack(neg_m, neg_m);
-                    psum = f2_pack(0.f, 0.f);
-                    mx0 = -INFINITY;
-                    mx1 = -INFINITY;
+                float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-                    for (int q2 = 0; q2 < 2; ++q2) {
-                        uint32_t pk[16];
+                for (int q2 = 0; q2 < 2; ++q2)
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            const float s0 = __uint_as_float(sr[q2][2 * i]), s1 = __uint_as_float(sr[q2][2 * i + 1]);
-                            float x0, x1, p0, p1;
-                            f2_unpack(f2_fma(f2_pack(s0, s1), c2, nm2), x0, x1);
-                            if ((kPolyPairMask >> (q2 * 16 + i)) & 1u) {
-                                exp2_poly2(x0, x1, p0, p1);
-                            } else {
-                                p0 = fast_exp2(x0);
-                                p1 = fast_exp2(x1);
-                            }
-                            if constexpr (kTrack) {
-                                if (i & 1) mx1 = max3(mx1, s0, s1);
-                                else mx0 = max3(mx0, s0, s1);
-                            }
-                            psum = f2_add(psum, f2_pack(p0, p1));
-                            pk[i] = Num<T>::pack(p0, p1);
-                        }
-                        tmem_st16(lane_base + col_sb + q2 * 16, pk);  // P overwrites its S (already in registers)
+                    for (int i = 0; i < 32; i += 4) {
+                        mx0 = max3(mx0, __uint_as_float(sr[q2][i]), __uint_as_float(sr[q2][i + 1]));
+                        mx1 = max3(mx1, __uint_as_float(sr[q2][i + 2]), __uint_as_float(sr[q2][i + 3]));
                     }
-                };
-                bool grow = false;
+                const float m_blk = fmaxf(mx0, mx1) * c;
+                // move the exponent base only when the maximum grew by more than the threshold
+                const bool grow = m_blk > m_used + kRescaleThreshold;
                 float alpha = 1.f;
-                exp_pass(BoolTag<true>{});
-                {
-                    const float m_blk = fmaxf(mx0, mx1) * c;
-                    if (__any_sync(0xffffffffu, !(m_blk <= m_used + kRescaleThreshold))) {
-                        // ---- the exact way (always taken on a tile's first sub-block)
-                        grow = m_blk > m_used + kRescaleThreshold;
-                        if (grow) {
-                            alpha = fast_exp2(m_used - m_blk);  // 0 on the first sub-block
-                            m_used = m_blk;
-                            den *= alpha;
+                if (grow) {
+                    alpha = fast_exp2(m_used - m_blk);  // 0 on the first sub-block
+                    m_used = m_blk;
+                    den *= alpha;
+                }
+                const float neg_m = -m_used;
+                const f32x2 c2 = f2_pack(c, c), nm2 = f2_pack(neg_m, neg_m);
+                f32x2 psum = f2_pack(0.f, 0.f);
+                KF_PROF(2);
+#pragma unroll
+                for (int q2 = 0; q2 < 2; ++q2) {
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        float x0, x1, p0, p1;
+                        f2_unpack(f2_fma(f2_pack(__uint_as_float(sr[q2][2 * i]), __uint_as_float(sr[q2][2 * i + 1])), c2, nm2),
+                                  x0, x1);
+                        if ((kPolyPairMask >> (q2 * 16 + i)) & 1u) {
+                            exp2_poly2(x0, x1, p0, p1);
+                        } else {
+                            p0 = fast_exp2(x0);
+                            p1 = fast_exp2(x1);
                         }
-                        exp_pass(BoolTag<false>{});
+                        psum = f2_add(psum, f2_pack(p0, p1));
+                        pk[i] = Num<T>::pack(p0, p1);
                     }
+                    tmem_st16(lane_base + col_sb + q2 * 16, pk);  // P overwrites its S (already in registers)
                 }
                 // Probe the next score buffer now: the probe is a shared-memory round trip whose latency
                 // overlaps the store completion and barrier traffic below.

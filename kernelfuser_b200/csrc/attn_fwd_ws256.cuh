@@ -28,11 +28,12 @@ constexpr int kW256KvBoxBytes = kSub * 128;           // 64 rows x 64 columns
 constexpr int kW256Stages = 2;
 template <int D> __host__ __device__ constexpr int ws1_q_bytes() { return (D / 64) * kBoxBytes; }            // 128 rows x D columns
 template <int D> __host__ __device__ constexpr int ws1_kv_tile_bytes() { return (D / 64) * kW256KvBoxBytes; } // 64 rows x D columns
-template <int D> __host__ __device__ constexpr int ws1_smem_bytes() {
-    return ws1_q_bytes<D>() + 2 * kW256Stages * ws1_kv_tile_bytes<D>() + 1024 + 512 + 512;  // tiles, alignment, barriers, inverse RMS of the Q rows
+template <int D> __host__ __device__ constexpr int ws1_smem_bytes(bool factored = false) {
+    // tiles, alignment slack, barriers (+ the inverse RMS of the Q rows in the factored form)
+    return ws1_q_bytes<D>() + 2 * kW256Stages * ws1_kv_tile_bytes<D>() + 1024 + 512 + (factored ? 512 : 0);
 }
 
-template <int D, typename T>
+template <int D, typename T, bool FACTORED = false>  // FACTORED: see attn_fwd_ws_kernel
 __global__ void __launch_bounds__(kW256Threads, (D == 128 ? 2 : 1))
 attn_fwd_ws1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
@@ -66,7 +67,7 @@ attn_fwd_ws1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     uint64_t* pv_done = bars + 14;  // [jj & 1]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
     volatile int* s_abort = reinterpret_cast<volatile int*>(bars + 17);
-    float* s_inv = reinterpret_cast<float*>(bars + 64);  // [row] inverse RMS of the raw Q rows (factored form)
+    [[maybe_unused]] float* s_inv = reinterpret_cast<float*>(bars + 64);  // [row] inverse RMS of the raw Q rows (factored form)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -126,15 +127,19 @@ attn_fwd_ws1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         const int row = m0 + r;
         {
             auto wait_q = [&]() { return mbar_wait_abortable(q_full, 0, s_abort); };
-            const bool ok = a.factored ? q_inv_coop<D, T>(smem_q, r, a, s_inv, wait_q)
-                            : a.fuse_q ? q_prologue_coop<D, T, 4>(smem_q, r, m0, a, wait_q) : wait_q();
+            bool ok;
+            if constexpr (FACTORED) ok = q_inv_coop<D, T>(smem_q, r, a, s_inv, wait_q);
+            else ok = a.fuse_q ? q_prologue_coop<D, T, 4>(smem_q, r, m0, a, wait_q) : wait_q();
             if (!ok) fail = kStatusWsQFull;
         }
-        float c = a.scale_log2e;
-        if (a.factored && !fail) {  // (a failed wait fails in every thread of the group alike)
-            named_barrier_sync(3, 128);
-            c *= s_inv[r];
+        float c_row = a.scale_log2e;
+        if constexpr (FACTORED) {
+            if (!fail) {  // (a failed wait fails in every thread of the group alike)
+                named_barrier_sync(3, 128);
+                c_row *= s_inv[r];
+            }
         }
+        const float c = c_row;
         if (!fail) {
             if constexpr (kQInTmem) {
                 // every row of the tile has been transformed by some thread of this group: make that

@@ -124,18 +124,18 @@ int launch_attn_basic(const CUtensorMap& mq, const CUtensorMap& mk, const CUtens
     return KF_OK;
 }
 
-template <typename T>
+template <typename T, bool FACTORED = false>
 int launch_attn_ws(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
                    const kf::AttnArgs& a, cudaStream_t st) {
-    auto kern = kf::attn_fwd_ws_kernel<T>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kf::kWsSmemBytes);
+    auto kern = kf::attn_fwd_ws_kernel<T, FACTORED>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (FACTORED ? kf::kWsSmemBytesFactored : kf::kWsSmemBytes));
     if (e != cudaSuccess) return fail(KF_ECUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
     const int G = a.Hq / a.Hkv;
     const long long n_mblk = (a.S + kf::kBM - 1) / kf::kBM;
     const long long upg = (G % 2 == 0) ? n_mblk * (G / 2) : ((n_mblk + 1) / 2) * G;
     const long long grid = upg * a.B * a.Hkv;
     if (grid > 0x7fffffffLL) return fail(KF_EINVAL, "too many tiles");
-    kern<<<(unsigned)grid, kf::kWsThreads, kf::kWsSmemBytes, st>>>(mq, mk, mv, mo, a);
+    kern<<<(unsigned)grid, kf::kWsThreads, (FACTORED ? kf::kWsSmemBytesFactored : kf::kWsSmemBytes), st>>>(mq, mk, mv, mo, a);
     e = cudaGetLastError();
     if (e != cudaSuccess) return fail(KF_ECUDA, "attention launch failed: %s", cudaGetErrorString(e));
     return KF_OK;
@@ -158,11 +158,11 @@ int launch_attn_ws2(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensor
     return KF_OK;
 }
 
-template <int D, typename T>
+template <int D, typename T, bool FACTORED = false>
 int launch_attn_ws1(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
                     const kf::AttnArgs& a, cudaStream_t st) {
-    auto kern = kf::attn_fwd_ws1_kernel<D, T>;
-    constexpr int smem = kf::ws1_smem_bytes<D>();
+    auto kern = kf::attn_fwd_ws1_kernel<D, T, FACTORED>;
+    constexpr int smem = kf::ws1_smem_bytes<D>(FACTORED);
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return fail(KF_ECUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
     const long long n_mblk = (a.S + kf::kBM - 1) / kf::kBM;
@@ -317,19 +317,29 @@ int attention_impl(const void* q, const void* kn, const void* v, const void* gam
         CUtensorMap mk64, mv64;  // K/V stream in 64-row tiles
         if (int r = make_map(&mk64, kn, dtype, B, Hkv, S, D, k_sb, k_sh, k_ss, 64)) return r;
         if (int r = make_map(&mv64, v, dtype, B, Hkv, S, D, v_sb, v_sh, v_ss, 64)) return r;
+        if (factored)
+            return dtype == KF_BF16 ? launch_attn_ws1<128, __nv_bfloat16, true>(mq, mk64, mv64, mo, a, st)
+                                    : launch_attn_ws1<128, __half, true>(mq, mk64, mv64, mo, a, st);
         return dtype == KF_BF16 ? launch_attn_ws1<128, __nv_bfloat16>(mq, mk64, mv64, mo, a, st)
                                 : launch_attn_ws1<128, __half>(mq, mk64, mv64, mo, a, st);
     }
     if (D == 128 && variant == 4)
         return dtype == KF_BF16 ? launch_attn_ws2<__nv_bfloat16>(mq, mk, mv, mo, a, st)
                                 : launch_attn_ws2<__half>(mq, mk, mv, mo, a, st);
-    if (D == 128 && variant == 2)
+    if (D == 128 && variant == 2) {
+        if (factored)
+            return dtype == KF_BF16 ? launch_attn_ws<__nv_bfloat16, true>(mq, mk, mv, mo, a, st)
+                                    : launch_attn_ws<__half, true>(mq, mk, mv, mo, a, st);
         return dtype == KF_BF16 ? launch_attn_ws<__nv_bfloat16>(mq, mk, mv, mo, a, st)
                                 : launch_attn_ws<__half>(mq, mk, mv, mo, a, st);
+    }
     if (D == 256 && (variant == 0 || variant == 2)) {
         CUtensorMap mk64, mv64;  // K/V stream in 64-row tiles
         if (int r = make_map(&mk64, kn, dtype, B, Hkv, S, D, k_sb, k_sh, k_ss, 64)) return r;
         if (int r = make_map(&mv64, v, dtype, B, Hkv, S, D, v_sb, v_sh, v_ss, 64)) return r;
+        if (factored)
+            return dtype == KF_BF16 ? launch_attn_ws1<256, __nv_bfloat16, true>(mq, mk64, mv64, mo, a, st)
+                                    : launch_attn_ws1<256, __half, true>(mq, mk64, mv64, mo, a, st);
         return dtype == KF_BF16 ? launch_attn_ws1<256, __nv_bfloat16>(mq, mk64, mv64, mo, a, st)
                                 : launch_attn_ws1<256, __half>(mq, mk64, mv64, mo, a, st);
     }
