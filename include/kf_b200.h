@@ -67,7 +67,7 @@ int kf_prepare_rows(const void* x, void* y, const void* gamma, const void* cos_t
  * kn is the prepared K from kf_prepare_rows; v is the raw V.
  * scale is the softmax scale (the reference passes D^-0.5).
  * variant: 0 = choose automatically (D = 256: kernel 2; D = 128: kernel 5 when
- * B*Hq*ceil(S/128) <= 1024 query tiles, else kernel 2),
+ * B*Hq*ceil(S/128) <= 2048 query tiles, else kernel 2),
  * 1 = baseline kernel (softmax and MMA serialised inside a CTA; any head dim),
  * 2 = pipelined, warp-specialised kernel (D = 128: two Q tiles per CTA;
  * D = 256: one), 3 = persistent pipelined kernel (D = 128), 4 = pipelined

@@ -37,6 +37,7 @@ struct AttnArgs {
     float eps;
     int causal, rope, hf_norm, fuse_q;
     int factored;  // factored no-RoPE form: q stays raw, scores are scaled by the row's inverse RMS
+    int sg_groups; // (batch, KV head) groups per super-group of the CTA order (see sg_decode)
     int* status;  // device status word: 0 = ok, else first failure code
 #ifdef KF_PROFILE
     long long* prof;  // per-role cycle counters of one CTA (profiling builds only)
@@ -121,6 +122,35 @@ __device__ __forceinline__ bool q_prologue_coop(uint8_t* smem_q, int gtid, int m
         }
     }
     return true;
+}
+
+// CTA order of the pipelined kernels.  The (batch, KV head) groups are cut into super-groups of
+// `sg_groups` groups whose K and V together fit comfortably in L2; inside a super-group the CTAs are
+// ordered heaviest query block first ACROSS its groups (all groups' last query blocks, then all
+// second-to-last ones, ...), super-groups follow one another.  CTAs that run together therefore still
+// stream a small set of K/V tensors through L2, while the heavy CTAs of every group start early: with
+// one group after the other, the last group's heaviest CTA starts when almost no other work is left and
+// becomes the tail of the launch (12 % of the time at 16 groups, 2 % at 128).
+//   cta            blockIdx.x
+//   per_level      CTAs of one group at one query-block level (query heads, or head pairs)
+//   n_levels       query-block levels per group
+// Returns the group, the level counted from the heaviest (0 = last query block) and the position in it.
+struct SgItem {
+    int grp, level, sub;
+};
+__device__ __forceinline__ SgItem sg_decode(int cta, int n_groups, int sg_groups, int n_levels, int per_level) {
+    const int per_sg = sg_groups * n_levels * per_level;  // CTAs of a full super-group
+    const int sg = cta / per_sg;
+    const int g0 = sg * sg_groups;
+    const int gs = min(sg_groups, n_groups - g0);          // groups of this super-group (the last may be short)
+    const int j = cta - sg * per_sg;
+    const int row = gs * per_level;                        // CTAs of one level of this super-group
+    SgItem it;
+    it.level = j / row;
+    const int rem = j - it.level * row;
+    it.grp = g0 + rem / per_level;
+    it.sub = rem % per_level;
+    return it;
 }
 
 // Factored no-RoPE form (the reference's `factored_attention_kernel`,

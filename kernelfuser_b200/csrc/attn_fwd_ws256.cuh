@@ -75,11 +75,10 @@ attn_fwd_ws1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const int G = a.Hq / a.Hkv;
     const int n_mblk = (a.S + kBM - 1) / kBM;
     const int n_sub_all = (a.S + kSub - 1) / kSub;
-    const int upg = n_mblk * G;  // CTAs per (batch, KV head)
-    const int grp = blockIdx.x / upg, rr = blockIdx.x % upg;
-    const int b = grp / a.Hkv, kh = grp % a.Hkv;
-    const int m0 = (n_mblk - 1 - rr / G) * kBM;
-    const int h = kh * G + rr % G;
+    const SgItem it = sg_decode(blockIdx.x, a.B * a.Hkv, a.sg_groups, n_mblk, G);  // heaviest query block first
+    const int b = it.grp / a.Hkv, kh = it.grp % a.Hkv;
+    const int m0 = (n_mblk - 1 - it.level) * kBM;
+    const int h = kh * G + it.sub;
     const int n_sub = a.causal ? min((m0 + kBM) / kSub, n_sub_all) : n_sub_all;
 
     if (tid == 0) {

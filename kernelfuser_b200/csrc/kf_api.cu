@@ -174,8 +174,13 @@ int launch_attn_ws1(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensor
     return KF_OK;
 }
 
+// K + V bytes of the groups whose CTAs are interleaved heaviest-first (a fraction of the 126 MB L2).
+constexpr long long kSuperGroupBytes = 48LL << 20;
+// Launches of up to this many CTAs per resident slot interleave their groups.
+constexpr long long kInterleaveMaxCtasPerSlot = 10;
+
 // Largest number of 128-row query tiles for which variant 0 picks the one-tile-per-CTA kernel at D = 128.
-constexpr long long kAutoOneTileMaxTiles = 1024;
+constexpr long long kAutoOneTileMaxTiles = 2048;
 
 int sm_count() {
     static int cached[64];
@@ -306,12 +311,34 @@ int attention_impl(const void* q, const void* kn, const void* v, const void* gam
         return dtype == KF_BF16 ? launch_attn_persist<__nv_bfloat16>(mq, mk64, mv64, mo, a, st)
                                 : launch_attn_persist<__half>(mq, mk64, mv64, mo, a, st);
     }
-    // Automatic choice at D = 128: with few query tiles the one-tile-per-CTA kernel (two CTAs per SM) fills
-    // the SMs and balances the causal tail better than the two-tiles-per-CTA kernel; measured on B200 it is
-    // 4-17 % faster up to about a thousand tiles and 3-5 % slower from about ten thousand.
+    // Automatic choice at D = 128: with few query tiles the one-tile-per-CTA kernel (two CTAs per SM, groups
+    // interleaved heaviest first) fills the SMs and keeps the causal tail short; measured on B200 it is 4-17 %
+    // faster than the two-tiles-per-CTA kernel up to about two thousand tiles, equal up to about eight
+    // thousand and 3-5 % slower from there.
     if (D == 128 && variant == 0) {
         const long long tiles = (long long)B * Hq * ((S + kf::kBM - 1) / kf::kBM);
         variant = tiles <= kAutoOneTileMaxTiles ? 5 : 2;
+    }
+    {
+        // CTA order (sg_decode).  Small launches - up to about ten CTAs per resident slot - interleave all
+        // their (batch, KV head) groups heaviest query block first, as far as the groups' K and V stay within
+        // kSuperGroupBytes of L2: otherwise the last group's heaviest CTA starts when almost nothing else is
+        // left and sticks out at the end (measured: 5-17 % of such a launch).  Large launches keep one group
+        // after the other: there the tail is small and interleaving costs 1-3 % of L2 locality.
+        const long long groups = (long long)B * Hkv;
+        const long long n_mblk = (S + kf::kBM - 1) / kf::kBM;
+        const int G = Hq / Hkv;
+        long long ctas_per_group = n_mblk * G;  // one 128-row tile per CTA
+        long long slots = sm_count();           // CTAs resident at a time
+        if (D == 128 && variant == 5) slots *= 2;
+        long long want = 1;
+        // (the two-tiles-per-CTA kernel of D = 128 only serves large launches and ignores sg_groups)
+        if (causal && groups * ctas_per_group <= kInterleaveMaxCtasPerSlot * slots) {
+            want = kSuperGroupBytes / (2LL * S * D * 2);  // K and V of one group, bytes
+            if (want < 1) want = 1;
+        }
+        const long long n_sg = (groups + want - 1) / want;
+        a.sg_groups = (int)((groups + n_sg - 1) / n_sg);
     }
     if (D == 128 && variant == 5) {
         CUtensorMap mk64, mv64;  // K/V stream in 64-row tiles
