@@ -67,7 +67,7 @@ int kf_prepare_rows(const void* x, void* y, const void* gamma, const void* cos_t
  * kn is the prepared K from kf_prepare_rows; v is the raw V.
  * scale is the softmax scale (the reference passes D^-0.5).
  * variant: 0 = choose automatically (D = 256: kernel 2; D = 128: kernel 5 when
- * B*Hq*ceil(S/128) <= 2048 query tiles, else kernel 2),
+ * B*Hq*ceil(S/128) <= 8192 query tiles, else kernel 2),
  * 1 = baseline kernel (softmax and MMA serialised inside a CTA; any head dim),
  * 2 = pipelined, warp-specialised kernel (D = 128: two Q tiles per CTA;
  * D = 256: one), 3 = persistent pipelined kernel (D = 128), 4 = pipelined
@@ -92,8 +92,9 @@ int kf_attention_fwd(const void* q, const void* kn, const void* v, const void* g
  * (one rounding); the RAW q feeds Q K^T and each query row's scores are scaled by
  * inv_rms(q_row) * scale * log2(e).  The reference keeps inv_rms(q) in a separate
  * FP32 tensor [B,Hq,S]; here it is computed in the attention prologue and stays on
- * chip, so there is no such argument.  No rotary tables in this form.  Opt-in: its
- * rounding points differ from kf_prepare_rows + kf_attention_fwd. */
+ * chip, so there is no such argument.  No rotary tables in this form.  variant as in
+ * kf_attention_fwd, restricted to 0, 2 and 5.  Opt-in: its rounding points differ from
+ * kf_prepare_rows + kf_attention_fwd. */
 int kf_factored_attention(const void* q, const void* k, const void* v, const void* gamma_q, const void* gamma_k,
                           void* kn, void* out, int B, int Hq, int Hkv, int S, int D, int dtype, int causal,
                           float eps, float scale,
@@ -102,7 +103,7 @@ int kf_factored_attention(const void* q, const void* k, const void* v, const voi
                           int64_t v_stride_b, int64_t v_stride_h, int64_t v_stride_s,
                           int64_t kn_stride_b, int64_t kn_stride_h, int64_t kn_stride_s,
                           int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s,
-                          int* status, void* stream);
+                          int* status, int variant, void* stream);
 
 /* Whole operator without any allocation (no counterpart in the reference,
  * whose wrapper always allocates its prepared-K scratch with torch.empty_like).

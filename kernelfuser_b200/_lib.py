@@ -42,7 +42,7 @@ def _declare(lib):
                                                   [c_void_p, c_void_p])
     lib.kf_factored_attention.restype = c_int
     lib.kf_factored_attention.argtypes = ([c_void_p] * 7 + [c_int] * 7 + [c_float] * 2 + [c_int64] * 15 +
-                                          [c_void_p, c_void_p])
+                                          [c_void_p, c_int, c_void_p])
     return lib
 
 

@@ -218,7 +218,7 @@ def fused(q, k, v, gq, gk, cos, sin, causal, eps=1e-6, scale=None, norm_style="q
     return flat
 
 
-def factored_attention(q, k, v, gq, gk, *, causal=False, eps=1e-6, scale=None, out=None, kn=None):
+def factored_attention(q, k, v, gq, gk, *, causal=False, eps=1e-6, scale=None, out=None, kn=None, variant=0):
     """No-RoPE attention in the reference's FACTORED form (``launch_factored_attention``,
     src/e1_qk_publication_v3.py:638-650): the query weight is folded into the prepared keys,
     ``KN = r(k * inv_rms(k) * gk * gq)``, the raw ``q`` feeds Q K^T and every query row's scores
@@ -247,7 +247,7 @@ def factored_attention(q, k, v, gq, gk, *, causal=False, eps=1e-6, scale=None, o
             _ptr(q), _ptr(k), _ptr(v), _ptr(gq), _ptr(gk), _ptr(kn), _ptr(out),
             b, hq, k.shape[1], s, d, _DTYPES[q.dtype], int(bool(causal)), float(eps), sc,
             *_strides3(q), *_strides3(k), *_strides3(v), *_strides3(kn), *_strides3(out),
-            st.data_ptr(), stream))
+            st.data_ptr(), int(variant), stream))
     return out
 
 

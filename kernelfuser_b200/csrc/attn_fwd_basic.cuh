@@ -38,6 +38,7 @@ struct AttnArgs {
     int causal, rope, hf_norm, fuse_q;
     int factored;  // factored no-RoPE form: q stays raw, scores are scaled by the row's inverse RMS
     int sg_groups; // (batch, KV head) groups per super-group of the CTA order (see sg_decode)
+    int sg_first;  // leading groups that run one after the other
     int* status;  // device status word: 0 = ok, else first failure code
 #ifdef KF_PROFILE
     long long* prof;  // per-role cycle counters of one CTA (profiling builds only)
@@ -130,7 +131,9 @@ __device__ __forceinline__ bool q_prologue_coop(uint8_t* smem_q, int gtid, int m
 // second-to-last ones, ...), super-groups follow one another.  CTAs that run together therefore still
 // stream a small set of K/V tensors through L2, while the heavy CTAs of every group start early: with
 // one group after the other, the last group's heaviest CTA starts when almost no other work is left and
-// becomes the tail of the launch (12 % of the time at 16 groups, 2 % at 128).
+// becomes the tail of the launch (12 % of the time at 16 groups, 2 % at 128).  Large launches interleave only
+// their last few groups (sg_first > 0): enough to keep the tail short without giving up the locality of the
+// group-major order for the bulk of the launch.
 //   cta            blockIdx.x
 //   per_level      CTAs of one group at one query-block level (query heads, or head pairs)
 //   n_levels       query-block levels per group
@@ -138,7 +141,20 @@ __device__ __forceinline__ bool q_prologue_coop(uint8_t* smem_q, int gtid, int m
 struct SgItem {
     int grp, level, sub;
 };
-__device__ __forceinline__ SgItem sg_decode(int cta, int n_groups, int sg_groups, int n_levels, int per_level) {
+__device__ __forceinline__ SgItem sg_decode(int cta, int n_groups, int sg_groups, int sg_first, int n_levels,
+                                            int per_level) {
+    // the first sg_first groups run one after the other (large launches interleave only their last groups)
+    const int upg = n_levels * per_level;
+    if (cta < sg_first * upg) {
+        SgItem it;
+        it.grp = cta / upg;
+        const int r = cta - it.grp * upg;
+        it.level = r / per_level;
+        it.sub = r - it.level * per_level;
+        return it;
+    }
+    cta -= sg_first * upg;
+    n_groups -= sg_first;
     const int per_sg = sg_groups * n_levels * per_level;  // CTAs of a full super-group
     const int sg = cta / per_sg;
     const int g0 = sg * sg_groups;
@@ -148,7 +164,7 @@ __device__ __forceinline__ SgItem sg_decode(int cta, int n_groups, int sg_groups
     SgItem it;
     it.level = j / row;
     const int rem = j - it.level * row;
-    it.grp = g0 + rem / per_level;
+    it.grp = sg_first + g0 + rem / per_level;
     it.sub = rem % per_level;
     return it;
 }

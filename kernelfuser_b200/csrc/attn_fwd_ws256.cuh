@@ -75,7 +75,7 @@ attn_fwd_ws1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const int G = a.Hq / a.Hkv;
     const int n_mblk = (a.S + kBM - 1) / kBM;
     const int n_sub_all = (a.S + kSub - 1) / kSub;
-    const SgItem it = sg_decode(blockIdx.x, a.B * a.Hkv, a.sg_groups, n_mblk, G);  // heaviest query block first
+    const SgItem it = sg_decode(blockIdx.x, a.B * a.Hkv, a.sg_groups, a.sg_first, n_mblk, G);  // heaviest query block first
     const int b = it.grp / a.Hkv, kh = it.grp % a.Hkv;
     const int m0 = (n_mblk - 1 - it.level) * kBM;
     const int h = kh * G + it.sub;

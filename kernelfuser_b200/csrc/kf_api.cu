@@ -180,7 +180,7 @@ constexpr long long kSuperGroupBytes = 48LL << 20;
 constexpr long long kInterleaveMaxCtasPerSlot = 10;
 
 // Largest number of 128-row query tiles for which variant 0 picks the one-tile-per-CTA kernel at D = 128.
-constexpr long long kAutoOneTileMaxTiles = 2048;
+constexpr long long kAutoOneTileMaxTiles = 8192;
 
 int sm_count() {
     static int cached[64];
@@ -311,10 +311,10 @@ int attention_impl(const void* q, const void* kn, const void* v, const void* gam
         return dtype == KF_BF16 ? launch_attn_persist<__nv_bfloat16>(mq, mk64, mv64, mo, a, st)
                                 : launch_attn_persist<__half>(mq, mk64, mv64, mo, a, st);
     }
-    // Automatic choice at D = 128: with few query tiles the one-tile-per-CTA kernel (two CTAs per SM, groups
-    // interleaved heaviest first) fills the SMs and keeps the causal tail short; measured on B200 it is 4-17 %
-    // faster than the two-tiles-per-CTA kernel up to about two thousand tiles, equal up to about eight
-    // thousand and 3-5 % slower from there.
+    // Automatic choice at D = 128: the one-tile-per-CTA kernel (two CTAs per SM, groups interleaved heaviest
+    // first) fills the SMs and keeps the causal tail short; measured on B200 it is 4-17 % faster than the
+    // two-tiles-per-CTA kernel up to about two thousand query tiles, 1-4 % faster up to about eight thousand
+    // and 2-5 % slower at sixteen thousand (C4), where the shared K/V stream of the tile pair pays.
     if (D == 128 && variant == 0) {
         const long long tiles = (long long)B * Hq * ((S + kf::kBM - 1) / kf::kBM);
         variant = tiles <= kAutoOneTileMaxTiles ? 5 : 2;
@@ -331,14 +331,25 @@ int attention_impl(const void* q, const void* kn, const void* v, const void* gam
         long long ctas_per_group = n_mblk * G;  // one 128-row tile per CTA
         long long slots = sm_count();           // CTAs resident at a time
         if (D == 128 && variant == 5) slots *= 2;
-        long long want = 1;
-        // (the two-tiles-per-CTA kernel of D = 128 only serves large launches and ignores sg_groups)
+        // (the two-tiles-per-CTA kernel of D = 128 only serves large launches and keeps the group-major order)
+        long long fit = kSuperGroupBytes / (2LL * S * D * 2);  // K and V of one group, bytes
+        if (fit < 1) fit = 1;
+        a.sg_groups = 1;
+        a.sg_first = 0;
         if (causal && groups * ctas_per_group <= kInterleaveMaxCtasPerSlot * slots) {
-            want = kSuperGroupBytes / (2LL * S * D * 2);  // K and V of one group, bytes
-            if (want < 1) want = 1;
+            const long long n_sg = (groups + fit - 1) / fit;
+            a.sg_groups = (int)((groups + n_sg - 1) / n_sg);
+        } else if (causal) {
+            // Only the last groups are interleaved: as many as give every slot about the work of the heaviest
+            // CTA (twice the average CTA of a causal group).
+            long long tail = (2 * slots + ctas_per_group - 1) / ctas_per_group;
+            if (tail > fit) tail = fit;
+            if (tail > groups) tail = groups;
+            if (tail > 1) {
+                a.sg_groups = (int)tail;
+                a.sg_first = (int)(groups - tail);
+            }
         }
-        const long long n_sg = (groups + want - 1) / want;
-        a.sg_groups = (int)((groups + n_sg - 1) / n_sg);
     }
     if (D == 128 && variant == 5) {
         CUtensorMap mk64, mv64;  // K/V stream in 64-row tiles
@@ -411,14 +422,15 @@ int kf_factored_attention(const void* q, const void* k, const void* v, const voi
                           void* kn, void* out, int B, int Hq, int Hkv, int S, int D, int dtype, int causal, float eps,
                           float scale, int64_t q_sb, int64_t q_sh, int64_t q_ss, int64_t k_sb, int64_t k_sh,
                           int64_t k_ss, int64_t v_sb, int64_t v_sh, int64_t v_ss, int64_t n_sb, int64_t n_sh,
-                          int64_t n_ss, int64_t o_sb, int64_t o_sh, int64_t o_ss, int* status, void* stream) {
+                          int64_t n_ss, int64_t o_sb, int64_t o_sh, int64_t o_ss, int* status, int variant,
+                          void* stream) {
     if (!gamma_q || !gamma_k) return fail(KF_EINVAL, "gamma_q and gamma_k must not be NULL");
     if (int r = prepare_impl(k, kn, gamma_k, gamma_q, nullptr, nullptr, B, Hkv, S, D, dtype, /*hf_norm=*/0, eps, k_sb,
                              k_sh, k_ss, n_sb, n_sh, n_ss, stream))
         return r;
     return attention_impl(q, kn, v, gamma_q, nullptr, nullptr, out, B, Hq, Hkv, S, D, dtype, causal, /*hf_norm=*/0,
                           /*fuse_q=*/1, eps, scale, q_sb, q_sh, q_ss, n_sb, n_sh, n_ss, v_sb, v_sh, v_ss, o_sb, o_sh,
-                          o_ss, status, /*variant=*/0, /*factored=*/1, stream);
+                          o_ss, status, variant, /*factored=*/1, stream);
 }
 
 }  // extern "C"

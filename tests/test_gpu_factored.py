@@ -38,8 +38,7 @@ def test_matches_reference_golden(causal):
 
 @pytest.mark.parametrize("b,s,hq,hkv,d,dtype,causal", [
     (2, 517, 8, 2, 128, torch.bfloat16, True),    # ragged tail, two heads per CTA
-    (1, 2048, 32, 8, 128, torch.bfloat16, True),  # 512 query tiles: the one-tile-per-CTA kernel
-    (2, 2100, 32, 8, 128, torch.bfloat16, True),  # 1088 query tiles: the two-tile kernel, ragged tail
+    (1, 2048, 32, 8, 128, torch.bfloat16, True),  # the one-tile-per-CTA kernel (automatic choice at this size)
     (2, 390, 6, 2, 128, torch.float16, False),    # odd group size
     (2, 517, 4, 2, 256, torch.bfloat16, True),    # D = 256: raw Q lives in TMEM
     (1, 200, 3, 1, 256, torch.float16, False),
@@ -50,6 +49,17 @@ def test_matches_oracle(b, s, hq, hkv, d, dtype, causal):
     ref = orc.oracle_fp32(q, k, v, gq, gk, None, None, causal)
     emu = orc.emulate_factored_attention(q, k, v, gq, gk, causal=causal)
     check(run(q, k, v, gq, gk, causal=causal), ref, emu, (b, s, hq, hkv, d, dtype, causal))
+
+
+@pytest.mark.parametrize("variant", [2, 5])
+def test_both_d128_kernels(variant):
+    # the two-tile kernel is the automatic choice only beyond 8192 query tiles: ask for it by number
+    q, k, v, gq, gk, _, _ = kf.make_inputs(2, 700, 8, 2, 128, seed=74, rope=False)
+    ref = orc.oracle_fp32(q, k, v, gq, gk, None, None, True)
+    emu = orc.emulate_factored_attention(q, k, v, gq, gk, causal=True)
+    check(run(q, k, v, gq, gk, causal=True, variant=variant), ref, emu, variant)
+    with pytest.raises(ValueError):
+        run(q, k, v, gq, gk, causal=True, variant=3)
 
 
 def test_prepared_keys_follow_the_factored_contract():
