@@ -38,8 +38,9 @@ METRIC = "Fused QKnorm+RoPE+attn prefill TFLOP/s"
 UNIT = "TFLOP/s"
 DTYPE_NAME = {torch.bfloat16: "bf16", torch.float16: "fp16", torch.float32: "fp32"}
 # DRAM bytes (read + write) of one attention launch per batch element, from the ncu capture
-# summarised in profiles/attn_fwd_ws_C4.md (306.6 MB at batch 4); keyed by (S, Hq, Hkv, D).
-NCU_DRAM_BYTES_PER_BATCH = {(4096, 32, 8, 128): 306.6e6 / 4}
+# summarised in profiles/attn_fwd_ws_C4.md (306.2 MB at batch 4) and profiles/attn_fwd_ws1_C5.md (198.6 MB at
+# batch 1); keyed by (S, Hq, Hkv, D).
+NCU_DRAM_BYTES_PER_BATCH = {(4096, 32, 8, 128): 306.2e6 / 4, (8192, 16, 8, 256): 198.6e6}
 
 
 # ----------------------------------------------------------------------------
@@ -338,7 +339,7 @@ def main():
             "roofline": {"kernel": "attention", "bound": "tensor", "achieved": attn_tf, "peak": peaks["bf16_tflops"],
                          "unit": "TFLOP/s", "frac": attn_tf / peaks["bf16_tflops"],
                          "traffic": NCU_DRAM_BYTES_PER_BATCH.get((w.S, w.Hq, w.Hkv, w.D), 0) * w.B / world or None,
-                         "traffic_source": "ncu dram read+write of one launch at batch 4, scaled by batch",
+                         "traffic_source": "ncu dram read+write of one launch of a small-batch case, scaled by batch",
                          "peak_source": f"{tag} (cuBLAS bf16 burst)", "ms_per_launch": t_attn,
                          "flops_per_launch": flops_rank},
             "roofline_prepare": {"kernel": "prepare_rows(K)", "bound": "hbm", "achieved": prep_gbs,
