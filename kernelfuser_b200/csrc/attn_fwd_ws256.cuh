@@ -1,23 +1,28 @@
-// Warp-specialised, pipelined tcgen05 flash-attention forward kernel for D = 256.
+// Warp-specialised, pipelined tcgen05 flash-attention forward kernel with ONE 128-row Q tile per CTA
+// (all of D = 256; D = 128 for launches of moderate size, two CTAs per SM).
 //
 // Same operator as the other attention kernels (reference: `attention_v2_kernel`,
 // src/e1_rope_publication_v1.py:609-649; Q prologue :619-623; rounding contract `_rows`
 // :551-582).  At head dim 256 the output accumulator alone takes 256 of the 512 TMEM columns,
-// so a CTA owns ONE 128-row Q tile:
+// so a CTA can own only one tile:
 //   TMEM   : two 64-column score buffers (columns 0..127) | O (columns 128..383) |
 //            Q as 16-bit pairs (columns 384..511): the prepared Q tile is copied from shared
 //            memory into TMEM once, so Q K^T takes its A operand from TMEM and only K is
 //            streamed from shared memory (an SS MMA with N = 64 re-reads 4 KB of Q per
 //            instruction and is shared-memory bound)
-//   smem   : Q 64 KB, K ring 2 x 32 KB (64 keys x 256), V ring 2 x 32 KB
+//   smem   : Q 64 KB, K ring 2 x 32 KB (64 keys x 256), V ring 2 x 32 KB; once Q is in TMEM its
+//            buffer is a third ring stage (one K and one V tile) until the epilogue stages O there
 //   warps  : 0-3 softmax + Q prologue + epilogue (thread r <-> row r), 4 TMA producer,
 //            5 MMA issuer (one elected lane)
+// At D = 128 the tile takes 256 TMEM columns (scores 128 | O 128) and 98 KB of shared memory, Q
+// stays in shared memory (SS Q K^T) and two CTAs share an SM.
 // The KV loop advances in sub-blocks of 64 keys with double-buffered scores exactly as in
 // attn_fwd_ws.cuh: Q K^T of sub-block j+1 is queued before the issuer waits for P of sub-block
 // j, P (16-bit) overwrites its score buffer and feeds O += P V from TMEM, V is an MN-major
-// shared-memory operand with N = 256.  CTAs are ordered (batch, KV head) major, heaviest query
-// block first, the query heads of a KV group adjacent, so the K/V tiles one CTA streams are
-// found in L2 by its neighbours (nothing else shares them: no cluster multicast).
+// shared-memory operand with N = D.  CTA order: sg_decode (attn_fwd_basic.cuh) - small launches
+// interleave their (batch, KV head) groups heaviest query block first, large ones only their last
+// groups; the K/V tiles one CTA streams are found in L2 by its neighbours (nothing else shares
+// them: no cluster multicast).
 #pragma once
 #include "attn_fwd_ws.cuh"
 
@@ -45,6 +50,9 @@ attn_fwd_ws1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     constexpr uint32_t kColQ = 384;  // D = 256 only: 128 columns = 256 16-bit values per row
     constexpr int kW256QBytes = ws1_q_bytes<D>();
     constexpr int kW256KvTileBytes = ws1_kv_tile_bytes<D>();
+    // K/V ring: two stages of their own; at D = 256 the Q buffer, free once the prepared Q has moved to TMEM,
+    // serves as a third (its 64 KB hold one K and one V tile) until the epilogue stages the output there.
+    constexpr int kNS = kQInTmem ? 3 : 2;
     constexpr uint32_t kIdescQK = umma_idesc(Num<T>::kFmt, 0, kBM, kSub);
     constexpr uint32_t kIdescPV = umma_idesc(Num<T>::kFmt, 1, kBM, D);
 
@@ -56,17 +64,20 @@ attn_fwd_ws1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     uint8_t* smem_k = smem + kW256QBytes;
     uint8_t* smem_v = smem_k + kW256Stages * kW256KvTileBytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem_v + kW256Stages * kW256KvTileBytes);
+    // shared-memory tile of ring stage s (the third stage lives in the Q buffer)
+    auto k_stage = [&](int s) { return s < kW256Stages ? smem_k + s * kW256KvTileBytes : smem_q; };
+    auto v_stage = [&](int s) { return s < kW256Stages ? smem_v + s * kW256KvTileBytes : smem_q + kW256KvTileBytes; };
     uint64_t* q_full = bars + 0;
     uint64_t* q_ready = bars + 1;   // 4 arrivals (one per softmax warp)
     uint64_t* k_full = bars + 2;    // [stage]
-    uint64_t* k_empty = bars + 4;   // [stage]
-    uint64_t* v_full = bars + 6;    // [stage]
-    uint64_t* v_empty = bars + 8;   // [stage]
-    uint64_t* s_full = bars + 10;   // [buffer]
-    uint64_t* p_ready = bars + 12;  // [buffer] 4 arrivals
-    uint64_t* pv_done = bars + 14;  // [jj & 1]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
-    volatile int* s_abort = reinterpret_cast<volatile int*>(bars + 17);
+    uint64_t* k_empty = bars + 5;   // [stage]
+    uint64_t* v_full = bars + 8;    // [stage]
+    uint64_t* v_empty = bars + 11;  // [stage]
+    uint64_t* s_full = bars + 14;   // [buffer]
+    uint64_t* p_ready = bars + 16;  // [buffer] 4 arrivals
+    uint64_t* pv_done = bars + 18;  // [jj & 1]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+    volatile int* s_abort = reinterpret_cast<volatile int*>(bars + 21);
     [[maybe_unused]] float* s_inv = reinterpret_cast<float*>(bars + 64);  // [row] inverse RMS of the raw Q rows (factored form)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -89,11 +100,14 @@ attn_fwd_ws1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         mbar_init(q_full, 1);
         mbar_init(q_ready, 4);
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < kNS; ++i) {
             mbar_init(k_full + i, 1);
             mbar_init(k_empty + i, 1);
             mbar_init(v_full + i, 1);
             mbar_init(v_empty + i, 1);
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
             mbar_init(s_full + i, 1);
             mbar_init(p_ready + i, 4);
             mbar_init(pv_done + i, 1);
@@ -296,18 +310,22 @@ attn_fwd_ws1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             int s = 0;
             uint32_t epar = 1;  // passes at once on the first turn of the ring
             for (int jj = 0; jj < n_sub; ++jj) {
+                // (the Q buffer becomes a stage only after the prepared Q has been copied to TMEM)
+                if (kNS > kW256Stages && jj == kW256Stages && !mbar_wait_abortable(q_ready, 0, s_abort)) { fail = kStatusWsQReady; break; }
                 if (!mbar_wait_abortable(k_empty + s, epar, s_abort)) { fail = kStatusWsKEmpty; break; }
                 mbar_expect_tx(k_full + s, kW256KvTileBytes);
+                uint8_t* kd = k_stage(s);
 #pragma unroll
                 for (int bx = 0; bx < NB; ++bx)
-                    tma_load_4d(smem_k + s * kW256KvTileBytes + bx * kW256KvBoxBytes, &tm_k, k_full + s, bx * 64, jj * kSub, kh, b);
+                    tma_load_4d(kd + bx * kW256KvBoxBytes, &tm_k, k_full + s, bx * 64, jj * kSub, kh, b);
                 if (!mbar_wait_abortable(v_empty + s, epar, s_abort)) { fail = kStatusWsVEmpty; break; }
                 mbar_expect_tx(v_full + s, kW256KvTileBytes);
+                uint8_t* vd = v_stage(s);
 #pragma unroll
                 for (int bx = 0; bx < NB; ++bx)
-                    tma_load_4d(smem_v + s * kW256KvTileBytes + bx * kW256KvBoxBytes, &tm_v, v_full + s, bx * 64, jj * kSub, kh, b);
+                    tma_load_4d(vd + bx * kW256KvBoxBytes, &tm_v, v_full + s, bx * 64, jj * kSub, kh, b);
                 kv_issued = jj + 1;
-                if (++s == kW256Stages) { s = 0; epar ^= 1; }
+                if (++s == kNS) { s = 0; epar ^= 1; }
             }
             if (fail) {
                 *s_abort = 1;
@@ -317,15 +335,24 @@ attn_fwd_ws1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     } else {
         // =================================================== MMA issuer
         if (elect_one()) {
-            const uint32_t k_addr = smem_u32(smem_k), v_addr = smem_u32(smem_v);
             const uint64_t qk_desc = umma_desc_sw128(0, 16, 1024);               // K-major operands (Q and K)
             const uint64_t v_desc = umma_desc_sw128(0, kW256KvBoxBytes, 1024);   // MN-major operand (V)
             const uint32_t qk_hi = static_cast<uint32_t>(qk_desc >> 32), v_hi = static_cast<uint32_t>(v_desc >> 32);
-            const uint32_t k_lo = static_cast<uint32_t>(qk_desc) | ((k_addr & 0x3FFFFu) >> 4);
-            const uint32_t v_lo = static_cast<uint32_t>(v_desc) | ((v_addr & 0x3FFFFu) >> 4);
+            uint32_t k_lo[kNS], v_lo[kNS];  // descriptor low words of the ring stages
+#pragma unroll
+            for (int st = 0; st < kNS; ++st) {
+                k_lo[st] = static_cast<uint32_t>(qk_desc) | ((smem_u32(k_stage(st)) & 0x3FFFFu) >> 4);
+                v_lo[st] = static_cast<uint32_t>(v_desc) | ((smem_u32(v_stage(st)) & 0x3FFFFu) >> 4);
+            }
             const uint32_t q_lo = static_cast<uint32_t>(qk_desc) | ((smem_u32(smem_q) & 0x3FFFFu) >> 4);
+            auto stage_lo = [&](const uint32_t (&lo)[kNS], int stage) {  // (no dynamic indexing of registers)
+                uint32_t r = lo[0];
+#pragma unroll
+                for (int st = 1; st < kNS; ++st) r = (stage == st) ? lo[st] : r;
+                return r;
+            };
             auto issue_qk = [&](int stage, int buf) {
-                const uint32_t ka = k_lo + stage * (kW256KvTileBytes >> 4);
+                const uint32_t ka = stage_lo(k_lo, stage);
                 const uint32_t d = tmem_base + buf * kSub;
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
@@ -339,7 +366,7 @@ attn_fwd_ws1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 }
             };
             auto issue_pv = [&](int stage, int buf, uint32_t accumulate) {
-                const uint32_t va = v_lo + stage * (kW256KvTileBytes >> 4);
+                const uint32_t va = stage_lo(v_lo, stage);
                 const uint32_t d = tmem_base + kColO;
                 const uint32_t pa = tmem_base + buf * kSub;
                 umma_ts_lohi(d, pa, va, v_hi, kIdescPV, accumulate);
@@ -357,7 +384,7 @@ attn_fwd_ws1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                     issue_qk(kst, jq & 1);
                     umma_commit(s_full + (jq & 1));
                     umma_commit(k_empty + kst);
-                    if (++kst == kW256Stages) { kst = 0; kpar ^= 1; }
+                    if (++kst == kNS) { kst = 0; kpar ^= 1; }
                 }
                 if (jj < 0) continue;
                 if (!mbar_wait_abortable(v_full + vst, vpar, s_abort)) { fail = kStatusWsVFull; break; }
@@ -366,7 +393,7 @@ attn_fwd_ws1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 issue_pv(vst, jj & 1, jj > 0 ? 1u : 0u);
                 umma_commit(pv_done + (jj & 1));
                 umma_commit(v_empty + vst);
-                if (++vst == kW256Stages) { vst = 0; vpar ^= 1; }
+                if (++vst == kNS) { vst = 0; vpar ^= 1; }
             }
             if (fail) {
                 *s_abort = 1;
@@ -383,9 +410,9 @@ attn_fwd_ws1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         // leave no copy in flight into this CTA's shared memory
         mbar_wait(q_full, 0);
 #pragma unroll
-        for (int s = 0; s < kW256Stages; ++s) {
+        for (int s = 0; s < kNS; ++s) {
             if (kv_issued > s) {
-                const int last_u = (kv_issued - 1 - s) / kW256Stages;
+                const int last_u = (kv_issued - 1 - s) / kNS;
                 mbar_wait(k_full + s, last_u & 1);
                 mbar_wait(v_full + s, last_u & 1);
             }
