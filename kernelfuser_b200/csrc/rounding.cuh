@@ -4,13 +4,18 @@
 // Follows the reference's `_rows` (src/e1_rope_publication_v1.py:551-582):
 //   inv = rsqrt(sum(x^2)/D + eps)                        (fp32)
 //   hf:      y = r(r(x*inv) * gamma)        legacy:  y = r(x*inv*gamma)
-//   rope:    out_j = r(r(y_j*cos_j) - r(p_j*sin_j))  for j <  D/2, p_j = y_{j+D/2}
-//            out_j = r(r(y_j*cos_j) + r(p_j*sin_j))  for j >= D/2, p_j = y_{j-D/2}
+//   rope:    out_j = r(y_j*cos_j - r(p_j*sin_j))  for j <  D/2, p_j = y_{j+D/2}
+//            out_j = r(y_j*cos_j + r(p_j*sin_j))  for j >= D/2, p_j = y_{j-D/2}
 // where r(.) rounds to the 16-bit storage type (nearest even) and cos_j/sin_j
-// are the table entries of the OUTPUT column j.
+// are the table entries of the OUTPUT column j.  The source spells the rotation
+// as r(r(y*c) -+ r(p*s)), but the reference's compiled kernels contract the
+// primary product into a fused multiply-add: on B200 the Triton arm's prepared K
+// equals the form above bit for bit (up to the summation order of the row's sum of
+// squares, ~1e-5 of the elements) and differs from the uncontracted spelling in
+// 12-23 % of the elements.  The contracted form is what this code reproduces.
 //
 // Every r(a op b) whose operands are already 16-bit values is ONE packed
-// 16-bit instruction (mul/add/sub .rn on bf16x2 / f16x2 round the exact result
+// 16-bit instruction (mul / fma .rn on bf16x2 / f16x2 round the exact result
 // once), so the contract costs about five instructions per element instead
 // of a convert round trip at every rounding point.
 #pragma once
@@ -46,6 +51,11 @@ template <> struct Num<__nv_bfloat16> {
         asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
         return r;
     }
+    __device__ static __forceinline__ uint32_t fma2(uint32_t a, uint32_t b, uint32_t c) {  // r(a*b + c)
+        uint32_t r;
+        asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+        return r;
+    }
 };
 template <> struct Num<__half> {
     static constexpr uint32_t kFmt = 0;
@@ -70,6 +80,11 @@ template <> struct Num<__half> {
     __device__ static __forceinline__ uint32_t sub2(uint32_t a, uint32_t b) {
         uint32_t r;
         asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+        return r;
+    }
+    __device__ static __forceinline__ uint32_t fma2(uint32_t a, uint32_t b, uint32_t c) {  // r(a*b + c)
+        uint32_t r;
+        asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
         return r;
     }
 };
@@ -137,8 +152,9 @@ __device__ __forceinline__ void transform_pair(uint4& lo, uint4& hi, float inv, 
         const uint32_t ya = norm2<T>(l[i], inv, gl[i], hf);
         const uint32_t yb = norm2<T>(h[i], inv, gh[i], hf);
         if (rope) {
-            l[i] = Num<T>::sub2(Num<T>::mul2(ya, cl[i]), Num<T>::mul2(yb, sl[i]));
-            h[i] = Num<T>::add2(Num<T>::mul2(yb, ch[i]), Num<T>::mul2(ya, sh[i]));
+            // (flipping both sign bits negates the rounded product exactly)
+            l[i] = Num<T>::fma2(ya, cl[i], Num<T>::mul2(yb, sl[i]) ^ 0x80008000u);
+            h[i] = Num<T>::fma2(yb, ch[i], Num<T>::mul2(ya, sh[i]));
         } else {
             l[i] = ya;
             h[i] = yb;

@@ -118,13 +118,34 @@ def oracle_fp32_explicit(q, k, v, gq, gk, cos=None, sin=None, causal=False, scal
 # --------------------------------------------------------------------------
 # Rounding-contract emulation of the reference's compiled arm
 # --------------------------------------------------------------------------
+def _round_once(v: torch.Tensor, dt: torch.dtype) -> torch.Tensor:
+    """Round fp64 values to ``dt`` (bf16/fp16) with a single rounding.  A plain
+    cast goes through fp32 and can round twice; rounding to ODD at fp32 first
+    (sticky last bit) makes the final nearest-even rounding exact."""
+    f = v.to(torch.float32)
+    err = v - f.double()
+    bits = f.view(torch.int32)
+    away = (err * torch.sign(f.double())) > 0          # |v| > |f|
+    fix = (err != 0) & ((bits & 1) == 0) & (f != 0)
+    bits = torch.where(fix, torch.where(away, bits + 1, bits - 1), bits)
+    return bits.view(torch.float32).to(dt)
+
+
 def emulate_rows(x, gamma, cos=None, sin=None, *, hf_norm=True, eps=EPS):
     """``_rows`` (src/e1_rope_publication_v1.py:551-582) on CPU.
 
     x: [..., S, D] in bf16/fp16; gamma [D]; cos/sin [S, D] in the same dtype.
-    Every ``r(.)`` below is a round-to-nearest-even to the input dtype, all
-    other arithmetic is fp32; the rotation uses the table entry of the OUTPUT
-    column j (both halves of the table are read, unlike the FP32 oracle).
+    Every ``r(.)`` below is a round-to-nearest-even to the input dtype; the
+    rotation uses the table entry of the OUTPUT column j (both halves of the
+    table are read, unlike the FP32 oracle).
+
+    The source reads ``r(r(y*c) -+ r(p*s))`` (:577-581), but the compiled kernel
+    contracts the primary product into a fused multiply-add, ``r(y*c -+ r(p*s))``:
+    measured on B200 (Triton 3.6) the arm's prepared K equals this form in all
+    but ~1e-5 of the elements (summation order of the row's sum of squares) and
+    differs from the uncontracted spelling in 12-23 % of them; the fixture
+    ``tests/golden/triton_arm_b200.npz`` holds outputs of the real arm.  The
+    fused step is evaluated in fp64 (exact product and sum) and rounded once.
     """
     dt = x.dtype
     r = lambda t: t.to(dt).float()
@@ -141,10 +162,9 @@ def emulate_rows(x, gamma, cos=None, sin=None, *, hf_norm=True, eps=EPS):
         partner = torch.cat([y[..., half:], y[..., :half]], dim=-1)
         c = cos.to(dt).float()
         s = sin.to(dt).float()
-        primary = r(y * c)
-        rotated = r(partner * s)
-        y = torch.cat([r(primary[..., :half] - rotated[..., :half]),
-                       r(primary[..., half:] + rotated[..., half:])], dim=-1)
+        rotated = r(partner * s).double()
+        rotated = torch.cat([-rotated[..., :half], rotated[..., half:]], dim=-1)
+        y = _round_once(y.double() * c.double() + rotated, dt)
     return y.to(dt)
 
 

@@ -37,9 +37,10 @@ def test_prepare_rows_matches_rounding_contract(d, dtype, style, rope):
                           None if sin is None else sin.to(dev), norm_style=style)
     torch.cuda.synchronize()
     frac, max_ulp = ulp_report(got, want)
-    # rsqrt and the sum order may differ in the last place: allow rare 1-ulp
-    # flips of a rounding decision, nothing larger than 2 spacings
-    assert frac < 5e-3 and max_ulp <= 2.01, (frac, max_ulp)
+    # rsqrt and the sum order may differ in the last place, which now and then flips one rounding
+    # decision.  Observed on B200 over all 32 parametrisations (and on 2x8x1500 rows): at most 8.5e-5
+    # of the elements differ, by at most 0.73 spacings here (1.26 on the larger tensors).
+    assert frac < 5e-4 and max_ulp <= 1.51, (frac, max_ulp)
 
 
 def test_prepare_rows_strided_views_and_poison():
@@ -53,7 +54,7 @@ def test_prepare_rows_strided_views_and_poison():
     torch.cuda.synchronize()
     want = orc.emulate_rows(k[:, 2:4], gk, cos, sin)
     frac, max_ulp = ulp_report(out[:, 2:4], want)
-    assert frac < 5e-3 and max_ulp <= 2.01
+    assert frac < 5e-4 and max_ulp <= 1.51
     assert torch.isnan(out[:, :2]).all() and torch.isnan(out[:, 4:]).all()
 
 
