@@ -40,10 +40,7 @@ struct AttnArgs {
     int sg_groups; // (batch, KV head) groups per super-group of the CTA order (see sg_decode)
     int sg_first;  // leading groups that run one after the other
     int* status;  // device status word: 0 = ok, else first failure code
-#ifdef KF_PROFILE
-    long long* prof;  // per-role cycle counters of one CTA (profiling builds only)
-    int prof_block;
-#endif
+    unsigned int* sched;  // persistent kernel: {next work item, CTAs that have left}; both 0 between launches
 };
 
 enum : int {

@@ -66,21 +66,26 @@ __device__ __forceinline__ void named_barrier_sync(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+// Barrier of `nthreads` threads that also returns the OR of their predicates: used to make the outcome of
+// per-thread bounded waits uniform across a group before the group meets at further barriers.
+__device__ __forceinline__ bool named_barrier_or(int id, int nthreads, bool pred) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %3, 0;\n\t"
+        "bar.red.or.pred p, %1, %2, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(r)
+        : "r"(id), "r"(nthreads), "r"(static_cast<uint32_t>(pred))
+        : "memory");
+    return r != 0;
+}
+
 __device__ __forceinline__ float max3(float a, float b, float c) {
     float r;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
     return r;
 }
-
-#ifdef KF_PROFILE
-#define KF_PROF_DECL long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long prof_t = clock64(); const long long prof_start = prof_t
-#define KF_PROF(slot) do { const long long _n = clock64(); prof_acc[slot] += _n - prof_t; prof_t = _n; } while (0)
-#define KF_PROF_FLUSH(role) do { if (a.prof != nullptr && blockIdx.x == a.prof_block) { prof_acc[7] = clock64() - prof_start; for (int _i = 0; _i < 8; ++_i) a.prof[(role) * 8 + _i] = prof_acc[_i]; } } while (0)
-#else
-#define KF_PROF_DECL do {} while (0)
-#define KF_PROF(slot) do {} while (0)
-#define KF_PROF_FLUSH(role) do {} while (0)
-#endif
 
 // ---- packed fp32 pairs (one instruction for two lanes of the FMA pipe)
 typedef unsigned long long f32x2;
@@ -192,14 +197,6 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     constexpr uint32_t kIdescPV = umma_idesc(Num<T>::kFmt, 1, kBM, D);
 
     if (*reinterpret_cast<volatile int*>(a.status) != 0) return;  // an earlier CTA failed: drain quickly
-#ifdef KF_PROFILE
-    const long long kernel_entry = clock64();
-    long long pe[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    long long pe_t = kernel_entry;
-#define KF_PE(slot) do { const long long _n = clock64(); pe[slot] += _n - pe_t; pe_t = _n; } while (0)
-#else
-#define KF_PE(slot) do {} while (0)
-#endif
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -307,7 +304,6 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             const uint32_t col_s = t * 128, col_o = 256 + t * 128;
             const int row = tl.m0 + r;
             // ---- Q prologue
-            KF_PE(0);
             {
                 auto wait_q = [&]() { return mbar_wait_abortable(q_full + t, 0, s_abort); };
                 bool ok;
@@ -315,13 +311,11 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                 else ok = a.fuse_q ? q_prologue_coop<D, T>(my_q, r, tl.m0, a, wait_q) : wait_q();
                 if (!ok) fail = kStatusWsQFull;
             }
-            KF_PE(1);
             if (!fail) {
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(q_ready + t);
             }
-            KF_PE(2);
             float m_used = -INFINITY, den = 0.f;
             float c_row = a.scale_log2e;
             if constexpr (FACTORED) {
@@ -332,7 +326,6 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             }
             const float c = c_row;
             bool s_known_ready = false;
-            KF_PROF_DECL;
             for (int jj = 0; jj < tl.nsub && !fail; ++jj) {
                 const int buf = jj & 1;
                 const int n0 = jj * kSub;
@@ -341,13 +334,10 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                 if (!s_known_ready &&
                     !mbar_wait_abortable(s_full + 2 * t + buf, (jj >> 1) & 1, s_abort)) { fail = kStatusWsSFull; break; }
                 tc_fence_after();
-                KF_PROF(0);
-                if (jj == 0) KF_PE(3);
                 uint32_t sr[2][32];
                 tmem_ld32(lane_base + col_sb, sr[0]);
                 tmem_ld32(lane_base + col_sb + 32, sr[1]);
                 tmem_wait_ld();
-                KF_PROF(1);
                 const bool need_mask = (n0 + kSub > a.S) || (a.causal && (n0 + kSub - 1 > tl.m0));
                 if (need_mask) {
 #pragma unroll
@@ -378,7 +368,6 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                 const float neg_m = -m_used;
                 const f32x2 c2 = f2_pack(c, c), nm2 = f2_pack(neg_m, neg_m);
                 f32x2 psum = f2_pack(0.f, 0.f);
-                KF_PROF(2);
 #pragma unroll
                 for (int q2 = 0; q2 < 2; ++q2) {
                     uint32_t pk[16];
@@ -405,8 +394,6 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                 float ps0, ps1;
                 f2_unpack(psum, ps0, ps1);
                 den += ps0 + ps1;
-                KF_PROF(3);
-                KF_PROF(4);
                 if (jj > 0 && __any_sync(0xffffffffu, grow)) {
                     // O may only be touched once the previous P V has completed.  (pv_done alternates
                     // between two barriers, so a phase cannot be lapped: P V of jj+1 needs this P.)
@@ -422,18 +409,13 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                         tmem_st32(lane_base + col_o + q4 * 32, o);
                     }
                 }
-                KF_PROF(5);
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(p_ready + 2 * t + buf);
-                KF_PROF(6);
             }
-            if ((warp & 3) == 0 && lane == 0) KF_PROF_FLUSH(t);
             // ---- epilogue: O / den -> 16-bit -> swizzled smem (this tile's Q buffer) -> TMA store
-            KF_PE(7);
             if (!fail && !mbar_wait_abortable(pv_done + 2 * t + ((tl.nsub - 1) & 1), ((tl.nsub - 1) >> 1) & 1, s_abort)) fail = kStatusWsODone;
-            KF_PE(4);
             if (!fail) {
                 tc_fence_after();
                 const float inv_den = 1.f / den;
@@ -457,7 +439,6 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                 }
                 fence_proxy_async_smem();
             }
-            KF_PE(5);
             if (fail) {
                 *s_abort = 1;
                 atomicCAS(a.status, 0, fail);
@@ -470,10 +451,6 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                 tma_store_commit();
                 tma_store_wait_read();  // the buffer must outlive the copy's reads; the writes drain on their own
             }
-            KF_PE(6);
-#ifdef KF_PROFILE
-            if (tid == 0 && a.prof != nullptr && blockIdx.x == a.prof_block) { pe[7] = clock64() - kernel_entry; for (int i = 0; i < 8; ++i) a.prof[32 + i] = pe[i]; }
-#endif
         }
     } else if (warp == 8) {
         // =================================================== TMA producer
@@ -529,7 +506,6 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 #pragma unroll
                 for (int ks = 1; ks < kSub / 16; ++ks) umma_ts_lohi(d, pa + ks * 8, va + ks * 128, v_hi, kIdescPV, 1u);
             };
-            KF_PROF_DECL;
             const int t = warp - 9;
             const int my_nsub = (t == 0) ? tile[0].nsub : tile[1].nsub;
             // scores of sub-block 0
@@ -542,7 +518,6 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                     umma_commit(s_full + 2 * t);
                 }
             }
-            KF_PROF(0);
             for (int jj = 0; jj < n_sub && !fail; ++jj) {
                 // ---- queue the scores of sub-block jj+1 (their buffer was released by P V of jj-1)
                 const int j1 = jj + 1;
@@ -554,30 +529,23 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                         !mbar_wait_abortable(k_full + st1, ((j1 >> 1) / kWsStages) & 1, s_abort)) { fail = kStatusWsKFull; break; }
                     if (j1 < my_nsub) {
                         tc_fence_after();
-                        KF_PROF(0);
                         issue_qk(t, j1);
                         umma_commit(s_full + 2 * t + (j1 & 1));
                     }
                     if ((j1 & 1) == 1) umma_commit(k_empty + st1);  // this tile is done with both halves of that K tile
-                    KF_PROF(1);
                 }
                 // ---- O += P V of sub-block jj
                 const int st0 = (jj >> 1) % kWsStages;
                 if ((jj & 1) == 0 &&
                     !mbar_wait_abortable(v_full + st0, ((jj >> 1) / kWsStages) & 1, s_abort)) { fail = kStatusWsVFull; break; }
                 if (jj < my_nsub) {
-                    KF_PROF(2);
                     if (!mbar_wait_abortable(p_ready + 2 * t + (jj & 1), (jj >> 1) & 1, s_abort)) { fail = kStatusWsPReady; break; }
                     tc_fence_after();
-                    KF_PROF(3);
                     issue_pv(t, jj);
                     umma_commit(pv_done + 2 * t + (jj & 1));
-                    KF_PROF(4);
                 }
                 if ((jj & 1) == 1 || jj == n_sub - 1) umma_commit(v_empty + st0);
-                KF_PROF(5);
             }
-            KF_PROF_FLUSH(2 + t);
             if (fail) {
                 *s_abort = 1;
                 atomicCAS(a.status, 0, fail);

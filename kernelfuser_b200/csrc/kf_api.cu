@@ -1,6 +1,7 @@
 // C-ABI entry points of libkf_b200 (declared in include/kf_b200.h): host-side
 // argument checks, TMA tensor-map encoding and kernel launches.  No device
 // allocation, no synchronisation, no exceptions across the boundary.
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -12,9 +13,17 @@
 #include "attn_fwd_basic.cuh"
 #include "attn_fwd_ws.cuh"
 #include "attn_fwd_persist.cuh"
-#include "attn_fwd_ws2.cuh"
 #include "attn_fwd_ws256.cuh"
 #include "prepare_rows.cuh"
+
+#ifdef KF_DEBUG
+extern "C" int kf_debug_read(int* host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, kf::g_ps_dbg, sizeof(int) * 148 * 16 * 4);
+}
+extern "C" int kf_debug_time(long long* host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, kf::g_ps_time, sizeof(long long) * 148 * 16 * 8);
+}
+#endif
 
 namespace {
 
@@ -141,23 +150,6 @@ int launch_attn_ws(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorM
     return KF_OK;
 }
 
-template <typename T>
-int launch_attn_ws2(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
-                   const kf::AttnArgs& a, cudaStream_t st) {
-    auto kern = kf::attn_fwd_ws2_kernel<T>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kf::kWs2SmemBytes);
-    if (e != cudaSuccess) return fail(KF_ECUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
-    const int G = a.Hq / a.Hkv;
-    const long long n_mblk = (a.S + kf::kBM - 1) / kf::kBM;
-    const long long upg = (G % 2 == 0) ? n_mblk * (G / 2) : ((n_mblk + 1) / 2) * G;
-    const long long grid = upg * a.B * a.Hkv;
-    if (grid > 0x7fffffffLL) return fail(KF_EINVAL, "too many tiles");
-    kern<<<(unsigned)grid, kf::kWs2Threads, kf::kWs2SmemBytes, st>>>(mq, mk, mv, mo, a);
-    e = cudaGetLastError();
-    if (e != cudaSuccess) return fail(KF_ECUDA, "attention launch failed: %s", cudaGetErrorString(e));
-    return KF_OK;
-}
-
 template <int D, typename T, bool FACTORED = false>
 int launch_attn_ws1(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
                     const kf::AttnArgs& a, cudaStream_t st) {
@@ -194,12 +186,36 @@ int sm_count() {
     return cached[dev];
 }
 
+// Work counters of the persistent kernel: {next item, CTAs that have left} per slot.  They live in the
+// library image (zero at load), the kernel's last CTA puts them back to zero, and launches take the slots in
+// turn, so that launches in flight on different streams of a device do not share one (up to kSchedSlots of them).
+constexpr int kSchedSlots = 64;
+__device__ unsigned int g_sched[kSchedSlots][2];
+
+int sched_slot(unsigned int** out) {
+    static unsigned int* base[64];
+    static std::atomic<unsigned int> turn{0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(KF_ECUDA, "cudaGetDevice failed");
+    if (base[dev] == nullptr) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_sched);
+        if (e != cudaSuccess || p == nullptr)
+            return fail(KF_ECUDA, "cudaGetSymbolAddress(work counters) failed: %s", cudaGetErrorString(e));
+        base[dev] = static_cast<unsigned int*>(p);
+    }
+    *out = base[dev] + 2 * (turn.fetch_add(1, std::memory_order_relaxed) % kSchedSlots);
+    return KF_OK;
+}
+
 template <typename T>
 int launch_attn_persist(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
-                        const kf::AttnArgs& a, cudaStream_t st) {
+                        const kf::AttnArgs& a0, cudaStream_t st) {
     auto kern = kf::attn_fwd_persist_kernel<T>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kf::kPsSmemBytes);
     if (e != cudaSuccess) return fail(KF_ECUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
+    kf::AttnArgs a = a0;
+    if (int r = sched_slot(&a.sched)) return r;
     const int G = a.Hq / a.Hkv;
     const long long n_mblk = (a.S + kf::kBM - 1) / kf::kBM;
     const long long upg = (G % 2 == 0) ? n_mblk * (G / 2) : ((n_mblk + 1) / 2) * G;
@@ -214,14 +230,6 @@ int launch_attn_persist(const CUtensorMap& mq, const CUtensorMap& mk, const CUte
 
 }  // namespace
 
-#ifdef KF_PROFILE
-static __device__ long long g_prof[2048];
-static int g_prof_block = 0;
-extern "C" void kf_prof_set_block(int b) { g_prof_block = b; }
-extern "C" int kf_prof_read(long long* host_out) {
-    return (int)cudaMemcpyFromSymbol(host_out, g_prof, sizeof(long long) * 2048);
-}
-#endif
 
 namespace {
 
@@ -276,7 +284,7 @@ int attention_impl(const void* q, const void* kn, const void* v, const void* gam
         if (!stride_ok(s)) return fail(KF_EALIGN, "strides must be non-negative multiples of 8 elements");
     if (q_ss < D || k_ss < D || v_ss < D || o_ss < D) return fail(KF_EINVAL, "row stride must be at least D");
     if (!(scale > 0.f) || !(scale < 1e30f)) return fail(KF_EINVAL, "scale must be positive and finite");
-    if (variant < 0 || variant > 5) return fail(KF_EINVAL, "variant must be 0..5");
+    if (variant < 0 || variant > 5 || variant == 4) return fail(KF_EINVAL, "variant must be 0, 1, 2, 3 or 5");
     if (int r = check_device()) return r;
 
     CUtensorMap mq, mk, mv, mo;
@@ -295,14 +303,6 @@ int attention_impl(const void* q, const void* kn, const void* v, const void* gam
     if (factored && (cos_table || sin_table)) return fail(KF_EINVAL, "the factored form has no rotary tables");
     if (factored && variant != 0 && variant != 2 && variant != 5)
         return fail(KF_EINVAL, "the factored form runs on kernels 0, 2 and 5 only");
-#ifdef KF_PROFILE
-    {
-        void* pp = nullptr;
-        cudaGetSymbolAddress(&pp, g_prof);
-        a.prof = static_cast<long long*>(pp);
-        a.prof_block = g_prof_block;
-    }
-#endif
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (D == 128 && variant == 3) {
         CUtensorMap mk64, mv64;  // the persistent kernel streams K/V in 64-row tiles
@@ -361,9 +361,6 @@ int attention_impl(const void* q, const void* kn, const void* v, const void* gam
         return dtype == KF_BF16 ? launch_attn_ws1<128, __nv_bfloat16>(mq, mk64, mv64, mo, a, st)
                                 : launch_attn_ws1<128, __half>(mq, mk64, mv64, mo, a, st);
     }
-    if (D == 128 && variant == 4)
-        return dtype == KF_BF16 ? launch_attn_ws2<__nv_bfloat16>(mq, mk, mv, mo, a, st)
-                                : launch_attn_ws2<__half>(mq, mk, mv, mo, a, st);
     if (D == 128 && variant == 2) {
         if (factored)
             return dtype == KF_BF16 ? launch_attn_ws<__nv_bfloat16, true>(mq, mk, mv, mo, a, st)
@@ -381,7 +378,7 @@ int attention_impl(const void* q, const void* kn, const void* v, const void* gam
         return dtype == KF_BF16 ? launch_attn_ws1<256, __nv_bfloat16>(mq, mk64, mv64, mo, a, st)
                                 : launch_attn_ws1<256, __half>(mq, mk64, mv64, mo, a, st);
     }
-    if (variant >= 2) return fail(KF_EINVAL, "variants 3, 4 and 5 support head dim 128 only");  // D == 256 here
+    if (variant >= 2) return fail(KF_EINVAL, "variants 3 and 5 support head dim 128 only");  // D == 256 here
     if (D == 128)
         return dtype == KF_BF16 ? launch_attn_basic<128, __nv_bfloat16>(mq, mk, mv, mo, a, st)
                                 : launch_attn_basic<128, __half>(mq, mk, mv, mo, a, st);
