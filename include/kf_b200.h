@@ -11,12 +11,21 @@
  * Conventions
  *   dtype      KF_BF16 or KF_FP16; every tensor of a call shares it.
  *   layout     tensors are [B, H, S, D] with D contiguous; batch, head and
- *              row strides are given in ELEMENTS and must be multiples of 8
- *              (16 bytes), base pointers 16-byte aligned.  D is 128 or 256.
+ *              row strides are given in ELEMENTS and must be positive
+ *              multiples of 8 (16 bytes), base pointers 16-byte aligned.  A
+ *              stride of 0 is accepted only for a dimension of size 1:
+ *              expanded (broadcast) views are refused with KF_EALIGN.
+ *              D is 128 or 256.
  *   tables     cos/sin are contiguous [S, D]; pass NULL for both to skip RoPE.
- *   status     optional device int32 (may be NULL only for kf_prepare_rows):
- *              stays 0 on success; a kernel whose bounded wait expired writes
- *              a positive code there and returns without hanging.
+ *   status     device int32 owned by the caller (may be NULL only for
+ *              kf_prepare_rows): stays 0 on success; a kernel whose bounded
+ *              wait expired writes a positive code there (first failure wins)
+ *              and returns without hanging.  The word is STICKY: while it is
+ *              non-zero every attention launch that is given it returns at
+ *              once without touching `out`, so that work queued behind a
+ *              failure drains quickly.  The caller reads the word after
+ *              synchronising and must set it back to 0 before launching
+ *              again.
  *   return     0 on success; a negative KF_E* code when an argument is
  *              rejected on the host (nothing was launched);
  *              kf_last_error() then describes the reason (thread-local).
@@ -71,10 +80,10 @@ int kf_prepare_rows(const void* x, void* y, const void* gamma, const void* cos_t
  * 1 = baseline kernel (softmax and MMA serialised inside a CTA; any head dim),
  * 2 = pipelined, warp-specialised kernel (D = 128: two Q tiles per CTA;
  * D = 256: one), 3 = persistent pipelined kernel (D = 128), 4 = pipelined
- * kernel with two softmax warps per 32 rows (D = 128), 5 = the one-tile-per-CTA
+ * kernel that advances in blocks of 128 keys (D = 128), 5 = the one-tile-per-CTA
  * pipelined kernel of D = 256 instantiated for D = 128 with two CTAs per SM.
- * 3 and 4 are measured alternatives that are slower than 2 on the prefill
- * workloads; 5 is faster than 2 on small problems and slower on large ones. */
+ * 3 and 4 are measured alternatives; 5 is faster than 2 on small problems and
+ * slower on large ones. */
 int kf_attention_fwd(const void* q, const void* kn, const void* v, const void* gamma_q,
                      const void* cos_table, const void* sin_table, void* out,
                      int B, int Hq, int Hkv, int S, int D, int dtype,
@@ -133,6 +142,14 @@ int kf_optimized_attention_static(const void* q, const void* k, const void* v, c
                                   int64_t v_stride_b, int64_t v_stride_h, int64_t v_stride_s,
                                   int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s,
                                   int* status, void* stream);
+
+/* Self-test of the failure path (no counterpart in the reference).  Launches
+ * one warp that waits, with the polling loop of the kernels' bounded waits, on
+ * a barrier nobody arrives on; after `limit_clocks` SM clocks (1 .. 2^31) it
+ * gives up, writes code 901 into *status and returns.  Nothing faults or
+ * hangs.  Lets a host check that it notices a non-zero status word and
+ * recovers from it. */
+int kf_selftest_wait_timeout(int* status, long long limit_clocks, void* stream);
 
 #ifdef __cplusplus
 }

@@ -2,9 +2,9 @@
 KernelFuser's ``optimized_attention``)."""
 from .api import (KernelStatusError, attention_forward, check_status, factored_attention, fused,  # noqa: F401
                   optimized_attention, optimized_attention_host, optimized_attention_static,
-                  prepare_rows, status_word)
+                  prepare_rows, release_host_pipelines, selftest_wait_timeout, status_word)
 from .inputs import WORKLOADS, Workload, make_inputs, make_workload_inputs, rope_tables  # noqa: F401
 
 __all__ = ["optimized_attention", "optimized_attention_host", "optimized_attention_static", "factored_attention", "fused", "prepare_rows", "attention_forward", "check_status",
-           "status_word", "KernelStatusError", "make_inputs", "make_workload_inputs", "rope_tables",
+           "status_word", "KernelStatusError", "selftest_wait_timeout", "release_host_pipelines", "make_inputs", "make_workload_inputs", "rope_tables",
            "WORKLOADS", "Workload"]

@@ -16,7 +16,8 @@ LIB_PATH = PKG / "libkf_b200.so"
 
 KF_BF16, KF_FP16 = 0, 1
 EXPORTS = ("kf_version", "kf_last_error", "kf_prepare_rows", "kf_attention_fwd",
-           "kf_static_scratch_bytes", "kf_optimized_attention_static", "kf_factored_attention")
+           "kf_static_scratch_bytes", "kf_optimized_attention_static", "kf_factored_attention",
+           "kf_selftest_wait_timeout")
 
 _lib = None
 
@@ -43,6 +44,8 @@ def _declare(lib):
     lib.kf_factored_attention.restype = c_int
     lib.kf_factored_attention.argtypes = ([c_void_p] * 7 + [c_int] * 7 + [c_float] * 2 + [c_int64] * 15 +
                                           [c_void_p, c_int, c_void_p])
+    lib.kf_selftest_wait_timeout.restype = c_int
+    lib.kf_selftest_wait_timeout.argtypes = [c_void_p, ctypes.c_longlong, c_void_p]
     return lib
 
 
@@ -51,11 +54,18 @@ def load(build_if_missing: bool = True):
     global _lib
     if _lib is not None:
         return _lib
+    from . import build as _build
     if not LIB_PATH.exists():
         if not build_if_missing:
             raise KernelLibraryError(f"{LIB_PATH} is missing; run `python -m kernelfuser_b200.build`")
-        from . import build as _build
         _build.build()
+    elif build_if_missing and _build.stale():
+        # a kernel source or the header is newer than the library: never test or run an old binary silently
+        if _build.have_nvcc():
+            _build.build()
+        else:
+            import warnings
+            warnings.warn(f"{LIB_PATH} is older than its sources and nvcc is not available to rebuild it")
     try:
         _lib = _declare(ctypes.CDLL(str(LIB_PATH)))
     except OSError as e:  # pragma: no cover - depends on the environment

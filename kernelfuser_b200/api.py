@@ -56,6 +56,18 @@ def check_status(device=None) -> None:
         raise KernelStatusError(f"kernel reported status {code} (a bounded wait expired)")
 
 
+def selftest_wait_timeout(limit_clocks: int = 100_000, device=None) -> None:
+    """Run the library's self-test of the failure path (``kf_selftest_wait_timeout``): one warp waits on a
+    barrier nobody arrives on and gives up after ``limit_clocks`` SM clocks, leaving code 901 in the
+    device's status word.  The next ``check_status()`` raises ``KernelStatusError`` and clears the word;
+    until then every attention launch on the device returns without doing anything."""
+    lib = _lib.load()
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        st = status_word(dev)
+        _call(lib.kf_selftest_wait_timeout(st.data_ptr(), int(limit_clocks), torch.cuda.current_stream().cuda_stream))
+
+
 def _strides3(t: torch.Tensor):
     return t.stride(0), t.stride(1), t.stride(2)
 
@@ -103,6 +115,18 @@ def attention_forward(q, kn, v, gq, cos, sin, out, *, causal, norm_style="hf", f
                                    *_strides3(q), *_strides3(kn), *_strides3(v), *_strides3(out),
                                    st.data_ptr(), int(variant) if variant else _default_variant(), stream))
     return out
+
+
+def _check_strided(q, k, v):
+    """Layout rules for the entry points that read strided q/k/v in place (head-transposed views of
+    [B,S,H,D] projections): contiguous head dimension, 16-byte aligned strides, no expanded dimension."""
+    for t in (q, k, v):
+        if t.ndim != 4:
+            continue  # reported by the shape checks
+        if t.stride(3) != 1 or any(st % 8 for st in t.stride()[:3]):
+            raise ValueError("q/k/v need a contiguous head dimension and 16-byte aligned strides")
+        if any(st == 0 and n > 1 for st, n in zip(t.stride()[:3], t.shape[:3])):
+            raise ValueError("q/k/v must not be expanded (stride 0 over a dimension larger than 1)")
 
 
 def _validate(q, k, v, gq, gk, cos, sin, mode, bn, norm_style, require_contiguous=True):
@@ -200,10 +224,8 @@ def fused(q, k, v, gq, gk, cos, sin, causal, eps=1e-6, scale=None, norm_style="q
         cos = cos.to(q.dtype).contiguous()
         sin = sin.to(q.dtype).contiguous()
     style = "legacy" if norm_style == "legacy" else "hf"
+    _check_strided(q, k, v)
     _validate(q, k, v, gq.contiguous(), gk.contiguous(), cos, sin, "query", 128, style, require_contiguous=False)
-    for t in (q, k, v):
-        if t.stride(3) != 1 or any(st % 8 for st in t.stride()[:3]):
-            raise ValueError("q/k/v need a contiguous head dimension and 16-byte aligned strides")
     b, hq, s, d = q.shape
     if out_layout == "bshd":
         flat = torch.empty((b, s, hq * d), dtype=q.dtype, device=q.device)
@@ -228,12 +250,10 @@ def factored_attention(q, k, v, gq, gk, *, causal=False, eps=1e-6, scale=None, o
     tensor does not exist here: the inverse RMS is computed in the attention prologue."""
     lib = _lib.load()
     gq, gk = gq.contiguous(), gk.contiguous()
+    _check_strided(q, k, v)
     _validate(q, k, v, gq, gk, None, None, "query", 128, "legacy", require_contiguous=False)
     if not (eps > 0):
         raise ValueError("eps must be positive")
-    for t in (q, k, v):  # head-transposed views of [B,S,H,D] projections are read in place
-        if t.stride(3) != 1 or any(st % 8 for st in t.stride()[:3]):
-            raise ValueError("q/k/v need a contiguous head dimension and 16-byte aligned strides")
     out = torch.empty(q.shape, dtype=q.dtype, device=q.device) if out is None else out
     kn = torch.empty(k.shape, dtype=k.dtype, device=k.device) if kn is None else kn
     if out.shape != q.shape or out.dtype != q.dtype or kn.shape != k.shape or kn.dtype != k.dtype:
@@ -296,7 +316,13 @@ class _HostPipeline:
         self.compute = torch.cuda.Stream(device=device)
 
 
-_pipelines = {}
+_pipelines = {}          # insertion-ordered: least recently used first
+_MAX_PIPELINES = 4       # staging-buffer sets kept; older ones are dropped (their device memory is freed)
+
+
+def release_host_pipelines() -> None:
+    """Drop the cached device staging buffers of ``optimized_attention_host``."""
+    _pipelines.clear()
 
 
 def optimized_attention_host(q, k, v, gq, gk, cos=None, sin=None, *, causal=False, norm_style="hf",
@@ -321,9 +347,12 @@ def optimized_attention_host(q, k, v, gq, gk, cos=None, sin=None, *, causal=Fals
     small = [None if t is None else t.to(dev, non_blocking=True) for t in (gq, gk, cos, sin)]
     qshape, kshape = (cb,) + tuple(q.shape[1:]), (cb,) + tuple(k.shape[1:])
     key = (dev, qshape, kshape, q.dtype)
-    pl = _pipelines.get(key)
+    pl = _pipelines.pop(key, None)
     if pl is None:
-        pl = _pipelines[key] = _HostPipeline(dev, qshape, kshape, q.dtype)
+        pl = _HostPipeline(dev, qshape, kshape, q.dtype)
+    _pipelines[key] = pl  # most recently used last
+    while len(_pipelines) > _MAX_PIPELINES:
+        _pipelines.pop(next(iter(_pipelines)))
     cur = torch.cuda.current_stream(dev)
     for st in (pl.h2d, pl.compute, pl.d2h):
         st.wait_stream(cur)  # the small tensors above, and any earlier use of the staging buffers

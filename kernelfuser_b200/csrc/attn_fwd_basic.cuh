@@ -209,7 +209,9 @@ attn_fwd_basic_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     constexpr uint32_t kIdescQK = umma_idesc(Num<T>::kFmt, 0, kBM, kBN);
     constexpr uint32_t kIdescPV = umma_idesc(Num<T>::kFmt, 1, kBM, D);
 
-    if (*reinterpret_cast<volatile int*>(a.status) != 0) return;  // an earlier CTA failed: drain quickly
+    // An earlier CTA or launch failed: drain quickly.  One thread reads the word and the whole CTA follows that
+    // reading, so no warp can leave while others go on to barriers the leaver would have served.
+    if (__syncthreads_or(threadIdx.x == 0 && *reinterpret_cast<volatile int*>(a.status) != 0)) return;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -279,7 +281,7 @@ attn_fwd_basic_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 
     // ---- Q prologue
     {
-        auto wait_q = [&]() { return mbar_wait(bar_q, 0); };
+        auto wait_q = [&]() { return __all_sync(0xffffffffu, mbar_wait(bar_q, 0)) != 0; };
         const bool ok = a.fuse_q ? q_prologue_coop<D, T, 4>(smem_q, tid, m0, a, wait_q) : wait_q();
         if (!ok) fail = kStatusWaitQ;
     }

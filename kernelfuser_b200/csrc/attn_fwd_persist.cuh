@@ -9,11 +9,13 @@
 // RMSNorm/RoPE transform, the first K/V copies, the conversion and store of the
 // output - are done by other warps than the ones the main loop waits for, one
 // item ahead (Q) or one item behind (output), so the tensor pipe does not idle
-// between items.
+// between items.  The next item is claimed only when the running one has a few
+// sub-blocks left: claiming earlier ties work to a CTA long before it can start
+// on it, which showed as a long tail on launches of few, heavy items.
 //
 // Roles (16 warps, registers re-balanced per warpgroup with setmaxnreg):
 //   warps 0-3 / 4-7   softmax of tile 0 / tile 1 (thread r <-> row r <-> TMEM lane r)
-//   warps 8-11        Q prologue of the item after next (RMSNorm + gamma + RoPE in
+//   warps 8-11        Q prologue of the next item (RMSNorm + gamma + RoPE in
 //                     place in shared memory) and epilogue of the finished item
 //                     (O / den -> 16-bit -> swizzled smem -> TMA store)
 //   warp  12          K/V producer (TMA into one ring of six 64-row stages, filled in
@@ -50,6 +52,7 @@ constexpr int kPsKvTileBytes = kSub * 128 * 2;    // 64 rows x 128 columns of 16
 constexpr int kPsKvBoxBytes = kSub * 128;         // one 64-column x 64-row box
 constexpr int kPsQSlotBytes = 2 * kWsTileBytes;   // both tiles of an item
 constexpr int kPsItemRing = 4;                    // published work items in flight
+constexpr int kPsClaimAhead = 8;                  // sub-blocks before the end of an item at which the next one is claimed
 constexpr int kPsCtrlBytes = 2048;                // barriers, item ring, row sums
 constexpr int kPsSmemBytes = 2 * kPsQSlotBytes + kPsRing * kPsKvTileBytes + 1024 + kPsCtrlBytes;
 
@@ -100,6 +103,7 @@ struct PsCtrl {
     uint64_t den_full[2];    // [tile] softmax group (4 arrivals) -> epilogue: row sums of the finished item are in `den`
     uint64_t item_full[kPsItemRing];   // scheduler -> every role
     uint64_t item_empty[kPsItemRing];  // every role -> scheduler (15 arrivals)
+    uint64_t near_end;       // softmax of tile 0 (1 arrival per item) -> scheduler: the item is about to finish
     uint32_t tmem_slot;
     int abort_flag;
     int item[kPsItemRing];
@@ -192,6 +196,7 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
             mbar_init(c->item_full + i, 1);
             mbar_init(c->item_empty + i, 15);  // 12 warps of the three warpgroup roles + K/V producer + 2 issuers
         }
+        mbar_init(&c->near_end, 1);
         c->abort_flag = 0;
         // an earlier launch or CTA failed: every thread of this CTA takes the same decision from this copy
         c->pad[0] = *reinterpret_cast<volatile int*>(a.status);
@@ -246,6 +251,9 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                 const int n0 = jj * kSub;
                 const uint32_t col_sb = col_s + buf * kSub;
                 KF_DBG(n, jj);
+                // tell the scheduler when this item has only a few sub-blocks left: only then does it claim the
+                // next one (claiming earlier would tie work to this CTA long before it can start on it)
+                if (tid == 0 && jj == max(0, my_nsub - kPsClaimAhead)) mbar_arrive(&c->near_end);
                 // (usually already known from the probe issued during the previous sub-block)
                 KF_TACC(2);
                 if (!s_known_ready &&
@@ -391,12 +399,15 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
             ++n_pro;
         };
         prologue();
-        if (more && !fail) prologue();
         for (int n = 0; !fail; ++n) {
             const int slot = n & 1;
             const int idx = (slot == 0) ? pending[0] : pending[1];
             if (idx < 0) break;
             if (slot == 0) pending[0] = -1; else pending[1] = -1;
+            // ---- prologue of item n + 1: it is published when item n is about to finish; its raw Q goes into
+            // the other slot, which the epilogue of item n - 1 released long ago
+            if (more) prologue();
+            if (fail) break;
             const PsItem it = ps_decode(idx, a);
             // ---- epilogue of item n: O / den -> 16-bit -> swizzled smem (the item's Q slot) -> TMA store
 #pragma unroll
@@ -452,8 +463,6 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                 tma_store_wait_read();  // the slot may be refilled once the copies have read it
                 mbar_arrive(c->q_empty + slot);
             }
-            // ---- prologue of item n + 2 (its raw Q is being copied into the slot just released)
-            if (more) prologue();
         }
         if (gtid == 0) tma_store_wait_all();
         KF_DBG_DUMP();
@@ -599,8 +608,11 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         } else {
             // ============================================ scheduler and raw-Q producer
             if (elect_one()) {
-                int nxt = blockIdx.x;  // the first item needs no counter
                 for (int n = 0; !fail; ++n) {
+                    // the first item needs no counter; later ones are claimed when the running item is about to
+                    // finish (its softmax group says so), so that no CTA sits on work it cannot start yet
+                    if (n > 0 && !mbar_wait_abortable(&c->near_end, (n - 1) & 1, s_abort)) { fail = kStatusPsItemEmpty; break; }
+                    const int nxt = n == 0 ? static_cast<int>(blockIdx.x) : static_cast<int>(gridDim.x + atomicAdd(a.sched, 1u));
                     const int idx = nxt < n_items ? nxt : -1;
                     const int rs = n & (kPsItemRing - 1);
                     KF_DBG(n, idx);
@@ -609,8 +621,6 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                     *reinterpret_cast<volatile int*>(c->item + rs) = idx;
                     mbar_arrive(c->item_full + rs);
                     if (idx < 0) break;
-                    // claim the next item now: the round trip of the atomic overlaps the waits below
-                    nxt = static_cast<int>(gridDim.x + atomicAdd(a.sched, 1u));
                     const PsItem it = ps_decode(idx, a);
                     const int slot = n & 1;
                     if (n >= 2 && !mbar_wait_abortable(c->q_empty + slot, ((n >> 1) - 1) & 1, s_abort)) { fail = kStatusPsQEmpty; break; }

@@ -196,7 +196,9 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     constexpr uint32_t kIdescQK = umma_idesc(Num<T>::kFmt, 0, kBM, 64 /* kSub */);
     constexpr uint32_t kIdescPV = umma_idesc(Num<T>::kFmt, 1, kBM, D);
 
-    if (*reinterpret_cast<volatile int*>(a.status) != 0) return;  // an earlier CTA failed: drain quickly
+    // An earlier CTA or launch failed: drain quickly.  One thread reads the word and the whole CTA follows that
+    // reading, so no warp can leave while others go on to barriers the leaver would have served.
+    if (__syncthreads_or(threadIdx.x == 0 && *reinterpret_cast<volatile int*>(a.status) != 0)) return;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -305,7 +307,8 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             const int row = tl.m0 + r;
             // ---- Q prologue
             {
-                auto wait_q = [&]() { return mbar_wait_abortable(q_full + t, 0, s_abort); };
+                // (all lanes of a warp wait together; the vote keeps them together if the wait runs out)
+                auto wait_q = [&]() { return __all_sync(0xffffffffu, mbar_wait_abortable(q_full + t, 0, s_abort)) != 0; };
                 bool ok;
                 if constexpr (FACTORED) ok = q_inv_coop<D, T>(my_q, r, a, s_inv + t * kBM, wait_q);
                 else ok = a.fuse_q ? q_prologue_coop<D, T>(my_q, r, tl.m0, a, wait_q) : wait_q();
@@ -319,10 +322,9 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             float m_used = -INFINITY, den = 0.f;
             float c_row = a.scale_log2e;
             if constexpr (FACTORED) {
-                if (!fail) {  // (a failed wait fails in every thread of the group alike)
-                    named_barrier_sync(1 + t, 128);
-                    c_row *= s_inv[t * kBM + r];
-                }
+                // every thread of the group takes part, whatever its wait returned, and all follow the vote
+                if (named_barrier_or(1 + t, 128, fail != 0)) { if (!fail) fail = kStatusWsQFull; }
+                else c_row *= s_inv[t * kBM + r];
             }
             const float c = c_row;
             bool s_known_ready = false;

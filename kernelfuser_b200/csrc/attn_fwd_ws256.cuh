@@ -56,7 +56,9 @@ attn_fwd_ws1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     constexpr uint32_t kIdescQK = umma_idesc(Num<T>::kFmt, 0, kBM, kSub);
     constexpr uint32_t kIdescPV = umma_idesc(Num<T>::kFmt, 1, kBM, D);
 
-    if (*reinterpret_cast<volatile int*>(a.status) != 0) return;  // an earlier CTA failed: drain quickly
+    // An earlier CTA or launch failed: drain quickly.  One thread reads the word and the whole CTA follows that
+    // reading, so no warp can leave while others go on to barriers the leaver would have served.
+    if (__syncthreads_or(threadIdx.x == 0 && *reinterpret_cast<volatile int*>(a.status) != 0)) return;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -139,7 +141,8 @@ attn_fwd_ws1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
         const int row = m0 + r;
         {
-            auto wait_q = [&]() { return mbar_wait_abortable(q_full, 0, s_abort); };
+            // (all lanes of a warp wait together; the vote keeps them together if the wait runs out)
+            auto wait_q = [&]() { return __all_sync(0xffffffffu, mbar_wait_abortable(q_full, 0, s_abort)) != 0; };
             bool ok;
             if constexpr (FACTORED) ok = q_inv_coop<D, T>(smem_q, r, a, s_inv, wait_q);
             else ok = a.fuse_q ? q_prologue_coop<D, T, 4>(smem_q, r, m0, a, wait_q) : wait_q();
@@ -147,17 +150,19 @@ attn_fwd_ws1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         }
         float c_row = a.scale_log2e;
         if constexpr (FACTORED) {
-            if (!fail) {  // (a failed wait fails in every thread of the group alike)
-                named_barrier_sync(3, 128);
-                c_row *= s_inv[r];
-            }
+            // every thread of the group takes part, whatever its wait returned, and all follow the vote
+            if (named_barrier_or(3, 128, fail != 0)) { if (!fail) fail = kStatusWsQFull; }
+            else c_row *= s_inv[r];
         }
         const float c = c_row;
+        if constexpr (kQInTmem) {
+            // Every row of the tile has been transformed by some thread of this group: make that visible before
+            // thread r copies row r into TMEM.  The barrier also makes the outcome of the wait uniform.
+            if (named_barrier_or(2, 128, fail != 0) && !fail) fail = kStatusWsQFull;
+        }
         if (!fail) {
             if constexpr (kQInTmem) {
-                // every row of the tile has been transformed by some thread of this group: make that
-                // visible, then thread r copies row r into TMEM columns [kColQ, kColQ + D/2)
-                named_barrier_sync(2, 128);
+                // thread r copies row r into TMEM columns [kColQ, kColQ + D/2)
                 const uint8_t* qrow = smem_q + r * 128;
                 const int sw = r & 7;
 #pragma unroll

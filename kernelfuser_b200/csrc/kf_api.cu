@@ -13,6 +13,7 @@
 #include "attn_fwd_basic.cuh"
 #include "attn_fwd_ws.cuh"
 #include "attn_fwd_persist.cuh"
+#include "attn_fwd_blk.cuh"
 #include "attn_fwd_ws256.cuh"
 #include "prepare_rows.cuh"
 
@@ -38,7 +39,10 @@ int fail(int code, const char* fmt, ...) {
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
-bool stride_ok(int64_t s) { return s >= 0 && (s % 8) == 0; }
+// Element stride of a dimension of extent n: a multiple of 8 (16 bytes), positive unless the dimension has a
+// single entry.  A zero stride over n > 1 entries (an expanded / broadcast view) is refused: the TMA maps
+// describe distinct rows and would walk past the allocation.
+bool stride_ok(int64_t s, int64_t n) { return (s % 8) == 0 && (s > 0 || (s == 0 && n == 1)); }
 
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -150,6 +154,23 @@ int launch_attn_ws(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorM
     return KF_OK;
 }
 
+template <typename T>
+int launch_attn_blk(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
+                    const kf::AttnArgs& a, cudaStream_t st) {
+    auto kern = kf::attn_fwd_blk_kernel<T>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kf::kWsSmemBytes);
+    if (e != cudaSuccess) return fail(KF_ECUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
+    const int G = a.Hq / a.Hkv;
+    const long long n_mblk = (a.S + kf::kBM - 1) / kf::kBM;
+    const long long upg = (G % 2 == 0) ? n_mblk * (G / 2) : ((n_mblk + 1) / 2) * G;
+    const long long grid = upg * a.B * a.Hkv;
+    if (grid > 0x7fffffffLL) return fail(KF_EINVAL, "too many tiles");
+    kern<<<(unsigned)grid, kf::kBlkThreads, kf::kWsSmemBytes, st>>>(mq, mk, mv, mo, a);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(KF_ECUDA, "attention launch failed: %s", cudaGetErrorString(e));
+    return KF_OK;
+}
+
 template <int D, typename T, bool FACTORED = false>
 int launch_attn_ws1(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
                     const kf::AttnArgs& a, cudaStream_t st) {
@@ -245,9 +266,9 @@ int prepare_impl(const void* x, void* y, const void* gamma, const void* gamma2, 
         return fail(KF_EINVAL, "provide both rotary tables or neither");
     if (!aligned16(x) || !aligned16(y) || !aligned16(gamma) || !aligned16(cos_table) || !aligned16(sin_table))
         return fail(KF_EALIGN, "pointers must be 16-byte aligned");
-    if (!stride_ok(x_sb) || !stride_ok(x_sh) || !stride_ok(x_ss) || !stride_ok(y_sb) || !stride_ok(y_sh) ||
-        !stride_ok(y_ss))
-        return fail(KF_EALIGN, "strides must be non-negative multiples of 8 elements");
+    if (!stride_ok(x_sb, B) || !stride_ok(x_sh, H) || !stride_ok(x_ss, S) || !stride_ok(y_sb, B) ||
+        !stride_ok(y_sh, H) || !stride_ok(y_ss, S))
+        return fail(KF_EALIGN, "strides must be positive multiples of 8 elements (0 only for a dimension of size 1)");
     if (x_ss < D || y_ss < D) return fail(KF_EINVAL, "row stride must be at least D");
     if (int r = check_device()) return r;
     kf::PrepareArgs a{};
@@ -280,11 +301,13 @@ int attention_impl(const void* q, const void* kn, const void* v, const void* gam
         !aligned16(cos_table) || !aligned16(sin_table))
         return fail(KF_EALIGN, "pointers must be 16-byte aligned");
     const int64_t strides[12] = {q_sb, q_sh, q_ss, k_sb, k_sh, k_ss, v_sb, v_sh, v_ss, o_sb, o_sh, o_ss};
-    for (int64_t s : strides)
-        if (!stride_ok(s)) return fail(KF_EALIGN, "strides must be non-negative multiples of 8 elements");
+    const int64_t extents[12] = {B, Hq, S, B, Hkv, S, B, Hkv, S, B, Hq, S};
+    for (int i = 0; i < 12; ++i)
+        if (!stride_ok(strides[i], extents[i]))
+            return fail(KF_EALIGN, "strides must be positive multiples of 8 elements (0 only for a dimension of size 1)");
     if (q_ss < D || k_ss < D || v_ss < D || o_ss < D) return fail(KF_EINVAL, "row stride must be at least D");
     if (!(scale > 0.f) || !(scale < 1e30f)) return fail(KF_EINVAL, "scale must be positive and finite");
-    if (variant < 0 || variant > 5 || variant == 4) return fail(KF_EINVAL, "variant must be 0, 1, 2, 3 or 5");
+    if (variant < 0 || variant > 5) return fail(KF_EINVAL, "variant must be 0..5");
     if (int r = check_device()) return r;
 
     CUtensorMap mq, mk, mv, mo;
@@ -361,6 +384,9 @@ int attention_impl(const void* q, const void* kn, const void* v, const void* gam
         return dtype == KF_BF16 ? launch_attn_ws1<128, __nv_bfloat16>(mq, mk64, mv64, mo, a, st)
                                 : launch_attn_ws1<128, __half>(mq, mk64, mv64, mo, a, st);
     }
+    if (D == 128 && variant == 4)
+        return dtype == KF_BF16 ? launch_attn_blk<__nv_bfloat16>(mq, mk, mv, mo, a, st)
+                                : launch_attn_blk<__half>(mq, mk, mv, mo, a, st);
     if (D == 128 && variant == 2) {
         if (factored)
             return dtype == KF_BF16 ? launch_attn_ws<__nv_bfloat16, true>(mq, mk, mv, mo, a, st)
@@ -388,9 +414,40 @@ int attention_impl(const void* q, const void* kn, const void* v, const void* gam
 
 }  // namespace
 
+namespace kf {
+constexpr int kStatusSelfTestWait = 901;
+// One warp waits on a barrier that nobody will ever arrive on, with the same polling loop as the kernels'
+// waits but a caller-given limit; when the limit runs out it records its code in the status word and
+// returns.  Nothing faults, traps or hangs: this is the failure path of every bounded wait in this library,
+// taken on purpose.
+__global__ void selftest_wait_kernel(int* status, long long limit_clocks) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    bool ok = mbar_try_wait(&bar, 0);
+    const long long t0 = clock64();
+    while (!ok && clock64() - t0 <= limit_clocks) ok = mbar_try_wait(&bar, 0);
+    ok = __all_sync(0xffffffffu, ok) != 0;
+    if (!ok && threadIdx.x == 0) atomicCAS(status, 0, kStatusSelfTestWait);
+}
+}  // namespace kf
+
 extern "C" {
 
-int kf_version(void) { return 100; }
+int kf_version(void) { return 101; }
+
+int kf_selftest_wait_timeout(int* status, long long limit_clocks, void* stream) {
+    if (!status) return fail(KF_EINVAL, "status must not be NULL");
+    if (limit_clocks < 1 || limit_clocks > (1ll << 31)) return fail(KF_EINVAL, "limit_clocks must be in [1, 2^31]");
+    if (int r = check_device()) return r;
+    kf::selftest_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(status, limit_clocks);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(KF_ECUDA, "self-test launch failed: %s", cudaGetErrorString(e));
+    return KF_OK;
+}
 
 const char* kf_last_error(void) { return g_err; }
 

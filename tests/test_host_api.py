@@ -58,6 +58,39 @@ def test_c_abi_rejects_bad_arguments_before_launch():
     assert rc == -1
     rc = lib.kf_attention_fwd(*args, 1, 4, 2, 8, 128, 0, 1, 1, 1, 1e-6, -1.0, *(st * 4), p, 0, None)
     assert rc == -1
+    # expanded (broadcast) views: a zero stride over a batch or head dimension larger than 1 is refused,
+    # for any of q / kn / v / out and for the row-prepare input; a size-1 dimension may carry stride 0
+    for which in range(4):
+        for dim in (0, 1):
+            strides = [list(st) for _ in range(4)]
+            strides[which][dim] = 0
+            flat = [x for t in strides for x in t]
+            rc = lib.kf_attention_fwd(*args, 2, 4, 2, 8, 128, 0, 1, 1, 1, 1e-6, 0.1, *flat, p, 0, None)
+            assert rc == -2 and b"size 1" in lib.kf_last_error(), (which, dim)
+    rc = lib.kf_prepare_rows(p, p, p, None, None, 2, 1, 8, 128, 0, 1, 1e-6, 0, 0, 128, 1024, 0, 128, None)
+    assert rc == -2
+    rc = lib.kf_selftest_wait_timeout(None, 1000, None)
+    assert rc == -1
+    rc = lib.kf_selftest_wait_timeout(p, 0, None)
+    assert rc == -1
+
+
+def test_expanded_views_are_refused_by_the_adapters():
+    # the strides are inspected on the host before any CUDA call
+    q, k, v, gq, gk, cos, sin = _inputs()
+    ke = k[:, :1].expand(-1, 2, -1, -1)  # stride 0 over two KV heads
+    for fn in (lambda: kf.fused(q, ke, v, gq, gk, cos, sin, True), lambda: kf.factored_attention(q, ke, v, gq, gk)):
+        with pytest.raises(ValueError, match="expanded"):
+            fn()
+
+
+def test_library_is_rebuilt_when_sources_change(tmp_path, monkeypatch):
+    from kernelfuser_b200 import build
+    assert not build.stale()  # the loaded library matches the tree
+    monkeypatch.setattr(build, "STAMP", tmp_path / "missing.srchash")
+    assert build.stale()
+    (tmp_path / "missing.srchash").write_text("0" * 64)
+    assert build.stale()
 
 
 def _inputs(**kw):
