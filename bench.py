@@ -37,10 +37,13 @@ from kernelfuser_b200.shard import head_shard, shard_inputs  # noqa: E402
 METRIC = "Fused QKnorm+RoPE+attn prefill TFLOP/s"
 UNIT = "TFLOP/s"
 DTYPE_NAME = {torch.bfloat16: "bf16", torch.float16: "fp16", torch.float32: "fp32"}
-# DRAM bytes (read + write) of one attention launch per batch element, from the ncu capture
-# summarised in profiles/attn_fwd_ws_C4.md (306.2 MB at batch 4) and profiles/attn_fwd_ws1_C5.md (198.6 MB at
-# batch 1); keyed by (S, Hq, Hkv, D).
-NCU_DRAM_BYTES_PER_BATCH = {(4096, 32, 8, 128): 306.2e6 / 4, (8192, 16, 8, 256): 198.6e6}
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch at the full single-GPU size of the
+# workload, from a one-launch ncu capture of this program (three metrics, --clock-control none); keyed by
+# (workload name, kernel).  None where no full-size capture has been taken.
+NCU_DRAM_BYTES_FULL = {
+    ("C4", "attention"): 807741952 + 504647168,   # read + write; algorithmic bytes 1 342 177 280
+    ("C4", "prepare"): 136419840 + 76488960,      # algorithmic bytes 268 435 456 (part of the output is still in L2)
+}
 
 
 # ----------------------------------------------------------------------------
@@ -134,13 +137,22 @@ def physical_gpu_index(local: int) -> int:
 
 
 # ----------------------------------------------------------------------------
-def cpu_oracle_rate(w, seconds_budget: float = 15.0, threads=None):
+def use_all_host_cores() -> int:
+    """Give torch's CPU kernels every core this process may run on.  Launchers such as torch.distributed.run
+    export OMP_NUM_THREADS=1 to their children, which would time the CPU arm on a single thread."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:  # pragma: no cover - non-Linux
+        n = os.cpu_count() or 1
+    torch.set_num_threads(max(n, 1))
+    return torch.get_num_threads()
+
+
+def cpu_oracle_rate(w, seconds_budget: float = 15.0):
     """Times the CPU FP32 oracle on a bounded sample (batch 1 of the workload)
     and returns (TFLOP/s, threads, description)."""
     from oracle import oracle as orc
-    if threads:
-        torch.set_num_threads(threads)
-    nthreads = torch.get_num_threads()
+    nthreads = use_all_host_cores()
     xs = make_workload_inputs(w, seed=0, B=1, dtype=torch.float32)
     flops = attention_flops(1, w.Hq, w.S, w.D, w.causal)
     orc.oracle_fp32(*xs, w.causal)  # warm-up
@@ -161,7 +173,7 @@ def run_reference(args, w, rank):
     if rank != 0:
         return
     from oracle import oracle as orc
-    nthreads = torch.get_num_threads()
+    nthreads = use_all_host_cores()
     xs = make_workload_inputs(w, seed=0, B=1, dtype=torch.float32)
     flops = attention_flops(1, w.Hq, w.S, w.D, w.causal)
     for _ in range(max(args.warmup, 1)):
@@ -201,6 +213,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--variant", type=int, default=0)
     ap.add_argument("--batch", type=int, default=0, help="override the workload batch (profiling on a smaller case)")
+    ap.add_argument("--no-graph", action="store_true", help="skip the graph-replay protocol")
+    ap.add_argument("--sustained-s", type=float, default=2.5, help="seconds of back-to-back steps (0 = skip)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
 
@@ -273,8 +287,9 @@ def main():
     torch.cuda.synchronize()
     kf.check_status(dev)
 
-    # ---- timed region: K steps, device time of the operator only (flush excluded)
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    # ---- timed region: K steps, device time of the operator only (flush excluded).  The operator call makes
+    # its two launches back to back (the attention kernel dependent on the prepare), so it is timed as a whole.
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(args.steps)]
     barrier()
     if sampler:
         sampler.mark_begin()
@@ -282,17 +297,26 @@ def main():
     for i in range(args.steps):
         flush.zero_()
         ev[i][0].record()
-        op_split(ev[i][1])
-        ev[i][2].record()
+        op()
+        ev[i][1].record()
     barrier()
     wall = time.perf_counter() - wall0
     if sampler:
         sampler.mark_end()
     clocks = sampler.stop() if sampler else None
     kf.check_status(dev)
-    t_prep = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
-    t_attn = sum(e[1].elapsed_time(e[2]) for e in ev) / args.steps
-    t_step = sum(e[0].elapsed_time(e[2]) for e in ev) / args.steps
+    t_step = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
+    # per-kernel times for the rooflines: the same two launches with an event between them (a few extra steps)
+    n_split = min(args.steps, 5)
+    ev2 = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(n_split)]
+    for i in range(n_split):
+        flush.zero_()
+        ev2[i][0].record()
+        op_split(ev2[i][1])
+        ev2[i][2].record()
+    torch.cuda.synchronize()
+    t_prep = sum(e[0].elapsed_time(e[1]) for e in ev2) / n_split
+    t_attn = sum(e[1].elapsed_time(e[2]) for e in ev2) / n_split
     times = torch.tensor([t_step, t_prep, t_attn], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
@@ -323,12 +347,78 @@ def main():
     h2d = sum(t.numel() * t.element_size() for t in host)
     d2h = host_out.numel() * host_out.element_size()
 
+    # ---- where the end-to-end time goes: this rank's copies alone, each direction by itself
+    def timed(fn, reps=3):
+        fn()
+        torch.cuda.synchronize()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        a0.record()
+        for _ in range(reps):
+            fn()
+        a1.record()
+        barrier()
+        return a0.elapsed_time(a1) / reps
+
+    def copy_in():
+        for d, h in zip((dq, dk, dv), host):
+            d.copy_(h, non_blocking=True)
+
+    t_h2d = timed(copy_in)
+    t_d2h = timed(lambda: host_out.copy_(out, non_blocking=True))
+    parts = torch.tensor([t_h2d, t_d2h], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(parts, op=dist.ReduceOp.MAX)
+    t_h2d, t_d2h = (float(x) for x in parts.tolist())
+
+    # ---- the reference's protocol beside the flushed per-step number: CUDA graphs of 20 back-to-back
+    # operator calls, fresh captures in each of 5 rounds, 7 replays per round, L2-warm (fixed buffers)
+    from kernelfuser_b200.timing import paired
+    gp = None
+    if not args.no_graph:
+        g = paired({"op": op}, rounds=5, samples=7, replays=20)
+        stats = torch.tensor([g["op"]["median_us"], g["op"]["p10_us"], g["op"]["p90_us"]], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        med, p10, p90 = (float(x) for x in stats.tolist())
+        gp = {"median_us": med, "p10_us": p10, "p90_us": p90, "tflops": flops_total / (med * 1e-6) / 1e12,
+              "protocol": g["protocol"], "reduction": "max over ranks of each statistic"}
+
+    # ---- sustained: the same step back to back for a few seconds (no flush), clocks and power sampled
+    sus = None
+    if args.sustained_s > 0:
+        n_sus = max(int(args.sustained_s * 1e3 / max(t_step, 1e-3)), 10)
+        s_sampler = ClockSampler(local, period_s=0.01) if rank == 0 else None
+        if s_sampler:
+            s_sampler.start()
+        barrier()
+        if s_sampler:
+            s_sampler.mark_begin()
+        b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        b0.record()
+        for _ in range(n_sus):
+            op()
+        b1.record()
+        barrier()
+        if s_sampler:
+            s_sampler.mark_end()
+        s_clocks = s_sampler.stop() if s_sampler else None
+        t_sus = torch.tensor([b0.elapsed_time(b1) / n_sus], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t_sus, op=dist.ReduceOp.MAX)
+        t_sus = float(t_sus.item())
+        kf.check_status(dev)
+        sus = {"steps": n_sus, "ms_per_step": t_sus, "seconds": n_sus * t_sus * 1e-3,
+               "value": flops_total / (t_sus * 1e-3) / 1e12, "unit": UNIT, "clocks": s_clocks}
+
     if rank == 0:
         peaks = load_peaks(ROOT)
         tag = "of measured" if peaks["source"] == "measured" else "of fallback"
         value = flops_total / (t_step * 1e-3) / 1e12
         attn_tf = flops_rank / (t_attn * 1e-3) / 1e12
         prep_b = prepare_bytes(w.B, sh.n_kv, w.S, w.D)
+        # algorithmic bytes of the attention launch: Q and O once, prepared K and V once (16-bit elements)
+        attn_bytes = 2.0 * w.B * w.S * w.D * (2 * sh.n_q + 2 * sh.n_kv)
         prep_gbs = prep_b / (t_prep * 1e-3) / 1e9
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -338,20 +428,31 @@ def main():
             "pct_of_nominal_bf16_peak": 100.0 * value / (2250.0 * world),
             "roofline": {"kernel": "attention", "bound": "tensor", "achieved": attn_tf, "peak": peaks["bf16_tflops"],
                          "unit": "TFLOP/s", "frac": attn_tf / peaks["bf16_tflops"],
-                         "traffic": NCU_DRAM_BYTES_PER_BATCH.get((w.S, w.Hq, w.Hkv, w.D), 0) * w.B / world or None,
-                         "traffic_source": "ncu dram read+write of one launch of a small-batch case, scaled by batch",
+                         "traffic": NCU_DRAM_BYTES_FULL.get((w.name, "attention")) if world == 1 else None,
+                         "algorithmic_bytes": attn_bytes,
+                         "traffic_source": "ncu dram read+write of one launch at this size (N=1 only)",
                          "peak_source": f"{tag} (cuBLAS bf16 burst)", "ms_per_launch": t_attn,
                          "flops_per_launch": flops_rank},
             "roofline_prepare": {"kernel": "prepare_rows(K)", "bound": "hbm", "achieved": prep_gbs,
                                  "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": prep_gbs / peaks["hbm_gbs"],
-                                 "traffic": None, "peak_source": tag, "ms_per_launch": t_prep,
+                                 "traffic": NCU_DRAM_BYTES_FULL.get((w.name, "prepare")) if world == 1 else None,
+                                 "peak_source": tag, "ms_per_launch": t_prep,
                                  "bytes_per_launch": prep_b},
             "e2e": {"value": flops_total / (t_e2e * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d * world,
-                    "d2h_bytes_per_step": d2h * world, "ms_per_step": t_e2e, "steps": e2e_steps},
-            "gpu_launches": 2 * args.steps,
+                    "d2h_bytes_per_step": d2h * world, "ms_per_step": t_e2e, "steps": e2e_steps,
+                    "breakdown_ms": {"h2d_alone": t_h2d, "d2h_alone": t_d2h, "kernels": t_step,
+                                     "note": "slowest rank; each direction copied by itself, all ranks at once"},
+                    "h2d_gbs_per_rank": h2d / (t_h2d * 1e-3) / 1e9, "d2h_gbs_per_rank": d2h / (t_d2h * 1e-3) / 1e9},
+            "gpu_launches": 2 * args.steps,  # row-prepare + attention per timed step
             "clocks": clocks,
             "wall_s_timed_region": wall,
         }
+        if gp is not None:
+            line["graph_protocol"] = gp
+        if sus is not None:
+            sus["frac_of_sustained_peak"] = sus["value"] / (peaks.get("bf16_tflops_sustained") or peaks["bf16_tflops"]) / world
+            sus["peak"] = peaks.get("bf16_tflops_sustained")
+            line["sustained"] = sus
         if world == 1 and not args.no_cpu_baseline:
             val, cores, desc = cpu_oracle_rate(w)
             line["cpu_baseline"] = {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc}

@@ -94,6 +94,22 @@ int kf_attention_fwd(const void* q, const void* kn, const void* v, const void* g
                      int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s,
                      int* status, int variant, void* stream);
 
+/* The whole operator in one call: kf_prepare_rows(k -> kn) followed by
+ * kf_attention_fwd(fuse_q = 1).  Replaces `launch_attention(mode='query')`
+ * (src/e1_rope_publication_v1.py:661-677), which makes the same two launches.
+ * `kn` ([B, Hkv, S, D], strides n_*) is the caller's scratch for the prepared
+ * K.  Same arguments and errors as the two separate calls. */
+int kf_optimized_attention(const void* q, const void* k, const void* v, const void* gamma_q, const void* gamma_k,
+                           const void* cos_table, const void* sin_table, void* kn, void* out,
+                           int B, int Hq, int Hkv, int S, int D, int dtype,
+                           int causal, int hf_norm, float eps, float scale,
+                           int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
+                           int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_s,
+                           int64_t v_stride_b, int64_t v_stride_h, int64_t v_stride_s,
+                           int64_t n_stride_b, int64_t n_stride_h, int64_t n_stride_s,
+                           int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s,
+                           int* status, int variant, void* stream);
+
 /* Factored no-RoPE form of the operator, both launches in one call.  Replaces
  * `launch_factored_attention` (src/e1_qk_publication_v3.py:638-650:
  * `prepare_factored_kernel` :593-611 + `factored_attention_kernel` :614-635).

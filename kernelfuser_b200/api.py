@@ -189,14 +189,21 @@ def optimized_attention(q, k, v, gq, gk, cos=None, sin=None, *, causal=False,
     if out.shape != q.shape or out.dtype != q.dtype or kn.shape != k.shape or kn.dtype != k.dtype:
         raise ValueError("out / kn must match q / k in shape and dtype")
     with torch.cuda.device(q.device):
-        prepare_rows(k, gk, cos, sin, norm_style=norm_style, eps=eps, out=kn)
         if mode == "unfused":
+            prepare_rows(k, gk, cos, sin, norm_style=norm_style, eps=eps, out=kn)
             qn = prepare_rows(q, gq, cos, sin, norm_style=norm_style, eps=eps)
             attention_forward(qn, kn, v, gq, cos, sin, out, causal=causal, norm_style=norm_style,
                               fuse_q=False, eps=eps, scale=scale, variant=variant)
         else:
-            attention_forward(q, kn, v, gq, cos, sin, out, causal=causal, norm_style=norm_style,
-                              fuse_q=True, eps=eps, scale=scale, variant=variant)
+            # one C call for both launches
+            b, hq, s, d = q.shape
+            sc = float(d ** -0.5 if scale is None else scale)
+            _call(_lib.load().kf_optimized_attention(
+                _ptr(q), _ptr(k), _ptr(v), _ptr(gq), _ptr(gk), _ptr(cos), _ptr(sin), _ptr(kn), _ptr(out),
+                b, hq, k.shape[1], s, d, _DTYPES[q.dtype], int(bool(causal)), int(norm_style == "hf"), float(eps), sc,
+                *_strides3(q), *_strides3(k), *_strides3(v), *_strides3(kn), *_strides3(out),
+                status_word(q.device).data_ptr(), int(variant) if variant else _default_variant(),
+                torch.cuda.current_stream().cuda_stream))
     return out
 
 

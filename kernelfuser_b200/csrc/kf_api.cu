@@ -5,6 +5,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <utility>
 
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -36,6 +37,16 @@ int fail(int code, const char* fmt, ...) {
     vsnprintf(g_err, sizeof(g_err), fmt, ap);
     va_end(ap);
     return code;
+}
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -131,8 +142,7 @@ int launch_attn_basic(const CUtensorMap& mq, const CUtensorMap& mk, const CUtens
     const long long n_mblk = (a.S + kf::kBM - 1) / kf::kBM;
     const long long grid = n_mblk * a.B * a.Hq;
     if (grid > 0x7fffffffLL) return fail(KF_EINVAL, "too many tiles");
-    kern<<<(unsigned)grid, 128, smem, st>>>(mq, mk, mv, mo, a);
-    e = cudaGetLastError();
+    e = launch_kernel(kern, dim3((unsigned)grid), dim3(128), smem, st, mq, mk, mv, mo, a);
     if (e != cudaSuccess) return fail(KF_ECUDA, "attention launch failed: %s", cudaGetErrorString(e));
     return KF_OK;
 }
@@ -148,8 +158,8 @@ int launch_attn_ws(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorM
     const long long upg = (G % 2 == 0) ? n_mblk * (G / 2) : ((n_mblk + 1) / 2) * G;
     const long long grid = upg * a.B * a.Hkv;
     if (grid > 0x7fffffffLL) return fail(KF_EINVAL, "too many tiles");
-    kern<<<(unsigned)grid, kf::kWsThreads, (FACTORED ? kf::kWsSmemBytesFactored : kf::kWsSmemBytes), st>>>(mq, mk, mv, mo, a);
-    e = cudaGetLastError();
+    e = launch_kernel(kern, dim3((unsigned)grid), dim3(kf::kWsThreads),
+                      (size_t)(FACTORED ? kf::kWsSmemBytesFactored : kf::kWsSmemBytes), st, mq, mk, mv, mo, a);
     if (e != cudaSuccess) return fail(KF_ECUDA, "attention launch failed: %s", cudaGetErrorString(e));
     return KF_OK;
 }
@@ -165,8 +175,7 @@ int launch_attn_blk(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensor
     const long long upg = (G % 2 == 0) ? n_mblk * (G / 2) : ((n_mblk + 1) / 2) * G;
     const long long grid = upg * a.B * a.Hkv;
     if (grid > 0x7fffffffLL) return fail(KF_EINVAL, "too many tiles");
-    kern<<<(unsigned)grid, kf::kBlkThreads, kf::kWsSmemBytes, st>>>(mq, mk, mv, mo, a);
-    e = cudaGetLastError();
+    e = launch_kernel(kern, dim3((unsigned)grid), dim3(kf::kBlkThreads), (size_t)kf::kWsSmemBytes, st, mq, mk, mv, mo, a);
     if (e != cudaSuccess) return fail(KF_ECUDA, "attention launch failed: %s", cudaGetErrorString(e));
     return KF_OK;
 }
@@ -181,8 +190,7 @@ int launch_attn_ws1(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensor
     const long long n_mblk = (a.S + kf::kBM - 1) / kf::kBM;
     const long long grid = n_mblk * a.B * a.Hq;
     if (grid > 0x7fffffffLL) return fail(KF_EINVAL, "too many tiles");
-    kern<<<(unsigned)grid, kf::kW256Threads, smem, st>>>(mq, mk, mv, mo, a);
-    e = cudaGetLastError();
+    e = launch_kernel(kern, dim3((unsigned)grid), dim3(kf::kW256Threads), (size_t)smem, st, mq, mk, mv, mo, a);
     if (e != cudaSuccess) return fail(KF_ECUDA, "attention launch failed: %s", cudaGetErrorString(e));
     return KF_OK;
 }
@@ -243,8 +251,8 @@ int launch_attn_persist(const CUtensorMap& mq, const CUtensorMap& mk, const CUte
     const long long items = upg * a.B * a.Hkv;
     if (items > 0x7fffffffLL) return fail(KF_EINVAL, "too many tiles");
     const int grid = (int)(items < sm_count() ? items : sm_count());
-    kern<<<grid, kf::kPsThreads, kf::kPsSmemBytes, st>>>(mq, mk, mv, mo, a, (int)items);
-    e = cudaGetLastError();
+    e = launch_kernel(kern, dim3((unsigned)grid), dim3(kf::kPsThreads), (size_t)kf::kPsSmemBytes, st, mq, mk, mv, mo, a,
+                      (int)items);
     if (e != cudaSuccess) return fail(KF_ECUDA, "attention launch failed: %s", cudaGetErrorString(e));
     return KF_OK;
 }
@@ -466,6 +474,25 @@ int kf_attention_fwd(const void* q, const void* kn, const void* v, const void* g
     return attention_impl(q, kn, v, gamma_q, cos_table, sin_table, out, B, Hq, Hkv, S, D, dtype, causal, hf_norm,
                           fuse_q, eps, scale, q_sb, q_sh, q_ss, k_sb, k_sh, k_ss, v_sb, v_sh, v_ss, o_sb, o_sh, o_ss,
                           status, variant, /*factored=*/0, stream);
+}
+
+// The whole operator in one call: row-prepare of K into the caller's `kn`, then the attention kernel - the
+// reference's `launch_attention(mode='query')` (src/e1_rope_publication_v1.py:661-677).  (Launching the
+// attention kernel programmatically dependent on the prepare was measured and dropped: its early CTAs compete
+// with the prepare's tail for memory bandwidth and the pair came out 2-3 % slower on the per-GPU shards.)
+int kf_optimized_attention(const void* q, const void* k, const void* v, const void* gamma_q, const void* gamma_k,
+                           const void* cos_table, const void* sin_table, void* kn, void* out, int B, int Hq, int Hkv,
+                           int S, int D, int dtype, int causal, int hf_norm, float eps, float scale, int64_t q_sb,
+                           int64_t q_sh, int64_t q_ss, int64_t k_sb, int64_t k_sh, int64_t k_ss, int64_t v_sb,
+                           int64_t v_sh, int64_t v_ss, int64_t n_sb, int64_t n_sh, int64_t n_ss, int64_t o_sb,
+                           int64_t o_sh, int64_t o_ss, int* status, int variant, void* stream) {
+    if (!gamma_q || !gamma_k) return fail(KF_EINVAL, "gamma_q and gamma_k must not be NULL");
+    if (int r = prepare_impl(k, kn, gamma_k, nullptr, cos_table, sin_table, B, Hkv, S, D, dtype, hf_norm, eps, k_sb,
+                             k_sh, k_ss, n_sb, n_sh, n_ss, stream))
+        return r;
+    return attention_impl(q, kn, v, gamma_q, cos_table, sin_table, out, B, Hq, Hkv, S, D, dtype, causal, hf_norm,
+                                 /*fuse_q=*/1, eps, scale, q_sb, q_sh, q_ss, n_sb, n_sh, n_ss, v_sb, v_sh, v_ss, o_sb,
+                                 o_sh, o_ss, status, variant, /*factored=*/0, stream);
 }
 
 // Factored no-RoPE form of the operator (the reference's `launch_factored_attention`,
