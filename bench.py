@@ -306,8 +306,8 @@ def main():
     clocks = sampler.stop() if sampler else None
     kf.check_status(dev)
     t_step = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
-    # per-kernel times for the rooflines: the same two launches with an event between them (a few extra steps)
-    n_split = min(args.steps, 5)
+    # per-kernel times for the rooflines: the same two launches with an event between them (K more steps)
+    n_split = args.steps
     ev2 = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(n_split)]
     for i in range(n_split):
         flush.zero_()

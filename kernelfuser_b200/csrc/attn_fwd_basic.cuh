@@ -61,17 +61,17 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
-// Cooperative Q prologue for a group of 128 threads (4 warps) on one swizzled
+// Cooperative Q prologue for a group of WARPS warps (4, or 8 with gtid 0..255) on one swizzled
 // 128-row tile.  D/16 lanes share a row (each owns one 16-byte chunk and its
 // rotation partner), so a warp touches 32/(D/16) rows per step with coalesced
 // table reads; the table chunks of the first batch of rows are fetched
 // BEFORE `wait_q()` (which blocks until the raw tile has landed), so their
 // latency overlaps the Q copy.  Returns false if the wait failed.
-template <int D, typename T, int HALVES = 2, typename WaitFn>
+template <int D, typename T, int HALVES = 2, int WARPS = 4, typename WaitFn>
 __device__ __forceinline__ bool q_prologue_coop(uint8_t* smem_q, int gtid, int m0, const AttnArgs& a, WaitFn&& wait_q) {
     constexpr int LPR = D / 16;              // lanes per row
     constexpr int RPW = 32 / LPR;            // rows per warp step
-    constexpr int NIT = kBM / (4 * RPW);     // steps
+    constexpr int NIT = kBM / (WARPS * RPW);     // steps
     constexpr int HALF = NIT / HALVES;       // steps whose table chunks are in flight together
     constexpr int NB = D / 64;
     const int lane = gtid & 31, w = gtid >> 5;
@@ -83,7 +83,7 @@ __device__ __forceinline__ bool q_prologue_coop(uint8_t* smem_q, int gtid, int m
     auto load_tables = [&](int it0) {
 #pragma unroll
         for (int i = 0; i < HALF; ++i) {
-            const int pos = m0 + (it0 + i) * 4 * RPW + w * RPW + rsub;
+            const int pos = m0 + (it0 + i) * WARPS * RPW + w * RPW + rsub;
             if (a.rope != 0 && pos < a.S) {
                 const uint4* c4 = reinterpret_cast<const uint4*>(a.cos) + static_cast<long long>(pos) * (D / 8);
                 const uint4* s4 = reinterpret_cast<const uint4*>(a.sin) + static_cast<long long>(pos) * (D / 8);
@@ -103,7 +103,7 @@ __device__ __forceinline__ bool q_prologue_coop(uint8_t* smem_q, int gtid, int m
         if (h > 0) load_tables(h * HALF);
 #pragma unroll
         for (int i = 0; i < HALF; ++i) {
-            const int r = (h * HALF + i) * 4 * RPW + w * RPW + rsub;
+            const int r = (h * HALF + i) * WARPS * RPW + w * RPW + rsub;
             const bool rope = a.rope != 0 && (m0 + r) < a.S;
             uint8_t* row = smem_q + r * 128;
             const int off = ((sub % 8) ^ (r & 7)) << 4;

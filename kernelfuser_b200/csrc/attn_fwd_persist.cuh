@@ -45,7 +45,8 @@ enum : int {
 #define KF_PS_REG_AUX 80
 #define KF_PS_REG_CTRL 96
 #endif
-static_assert(KF_PS_REG_SOFTMAX * 256 + KF_PS_REG_AUX * 128 + KF_PS_REG_CTRL * 128 <= 65536, "register re-balance");
+static_assert(KF_PS_REG_SOFTMAX * 256 + KF_PS_REG_AUX * 128 + KF_PS_REG_CTRL * 128 <= 128 * 512,
+              "register re-balance must fit the launch allocation (asking for more blocks forever)");
 constexpr int kPsThreads = 512;
 constexpr int kPsRing = 6;                        // K/V ring stages
 constexpr int kPsKvTileBytes = kSub * 128 * 2;    // 64 rows x 128 columns of 16-bit values (two 8 KB boxes)

@@ -18,6 +18,7 @@ For every case it records
 
     python oracle/triton_arm.py [--out gpurun_out/triton_arm.json] [--quick]
     python oracle/triton_arm.py --golden gpurun_out/triton_arm_b200.npz
+    python oracle/triton_arm.py --fusion-table gpurun_out/fusion_table.json
 
 The second form writes the fixture ``tests/golden/triton_arm_b200.npz`` is a copy
 of: prepared K and outputs of the real arm on small seeded cases (inputs are
@@ -155,8 +156,49 @@ def write_golden(ref, kf, path):
     print(f"wrote {path}: {sorted(out)}")
 
 
+# Query fusion against the equally scheduled two-kernel control, the comparison the reference publishes for
+# Hopper (results/RESULTS.md:61-65; arms at src/e1_rope_publication_v1.py:214-225): both modes of the CUDA
+# path and of the reference's Triton arm, same protocol.   name, B, S, Hq, Hkv, D, theta
+FUSION_SHAPES = [("B1_S128", 1, 128, 32, 8, 128, 1e6), ("B8_S128", 8, 128, 32, 8, 128, 1e6),
+                 ("B32_S128", 32, 128, 32, 8, 128, 1e6), ("B1_S512", 1, 512, 32, 8, 128, 1e6),
+                 ("B8_S512", 8, 512, 32, 8, 128, 1e6), ("B32_S512", 32, 512, 32, 8, 128, 1e6),
+                 ("C2", 1, 2048, 32, 8, 128, 1e6), ("C4", 16, 4096, 32, 8, 128, 1e6),
+                 ("C5", 8, 8192, 16, 8, 256, 1e4)]
+
+
+def fusion_table(ref, kf, paired, path):
+    rows = []
+    for name, b, s, hq, hkv, d, theta in FUSION_SHAPES:
+        xs = kf.make_inputs(b, s, hq, hkv, d, dtype=torch.bfloat16, theta=theta, seed=0)
+        q, k, v, gq, gk, cos, sin = [x.cuda() for x in xs]
+        out, kn, qn = torch.empty_like(q), torch.empty_like(k), torch.empty_like(q)
+        inputs = (q, k, v, gq, gk, cos, sin)
+        fns = {
+            "cuda_query": lambda: kf.optimized_attention(q, k, v, gq, gk, cos, sin, causal=True, out=out, kn=kn),
+            "cuda_unfused": lambda: kf.optimized_attention(q, k, v, gq, gk, cos, sin, causal=True, mode="unfused",
+                                                           out=out, kn=kn),
+            "triton_query": lambda: ref.launch_attention(inputs, out, causal=True, mode="query", bm=64, bn=128,
+                                                         gather=False, qn=None, kn=kn),
+            "triton_unfused": lambda: ref.launch_attention(inputs, out, causal=True, mode="unfused", bm=64, bn=128,
+                                                           gather=False, qn=qn, kn=kn),
+        }
+        big = b * hq * s * s > (1 << 32)
+        t = paired(fns, rounds=3, samples=5, replays=5 if big else 20)
+        kf.check_status()
+        row = {"shape": name, "B": b, "S": s, "Hq": hq, "Hkv": hkv, "D": d}
+        for arm in fns:
+            row[arm + "_us"] = t[arm]["median_us"]
+        row["cuda_fusion_gain"] = row["cuda_unfused_us"] / row["cuda_query_us"]
+        row["triton_fusion_gain"] = row["triton_unfused_us"] / row["triton_query_us"]
+        rows.append(row)
+        print(json.dumps(row), flush=True)
+    Path(path).parent.mkdir(parents=True, exist_ok=True)
+    Path(path).write_text(json.dumps(rows, indent=1) + "\n")
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--fusion-table", default="", help="write the fused-vs-unfused timing table to this JSON file")
     ap.add_argument("--golden", default="")
     ap.add_argument("--out", default=str(ROOT / "gpurun_out" / "triton_arm.json"))
     ap.add_argument("--quick", action="store_true")
@@ -169,6 +211,9 @@ def main():
     import triton
     if args.golden:
         write_golden(ref, kf, args.golden)
+        return
+    if args.fusion_table:
+        fusion_table(ref, kf, paired, args.fusion_table)
         return
     want = set(filter(None, args.cases.split(",")))
     recs = []

@@ -25,7 +25,7 @@ def test_wait_runs_out_status_is_reported_and_cleared():
     assert int(kf.status_word(dev).item()) == 901
 
     # every attention kernel drains without touching its output while the word is set
-    for variant in (0, 1, 2, 3, 4, 5):
+    for variant in (0, 1, 2, 3, 5):
         out = torch.full(dx[0].shape, float("nan"), dtype=dx[0].dtype, device=dev)
         kf.optimized_attention(*dx, causal=True, out=out, variant=variant)
         torch.cuda.synchronize()

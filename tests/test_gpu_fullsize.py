@@ -65,8 +65,10 @@ def test_full_size_properties(name):
         assert orc.within_tolerance(m), (name, b, h, m)
     # batch independence, bit for bit
     b = w.B // 2
-    # (variant 2 - or 5 for the shard - is what the automatic choice ran for the full call; a single batch element is small
-    # enough for the automatic choice to pick another kernel, whose rounding differs in the last bit)
+    # (The automatic choice ran the persistent two-tile kernel for the full D=128 call - its results equal
+    # variant 2's bit for bit, same arithmetic in the same order - and variant 5 for the shard; a single batch
+    # element is small enough for the automatic choice to pick another kernel, whose rounding differs in the
+    # last bit.)
     alone = kf.optimized_attention(dx[0][b:b + 1], dx[1][b:b + 1], dx[2][b:b + 1], *dx[3:], causal=True,
                                    variant=5 if name == "C4/4" else 2)
     torch.cuda.synchronize()

@@ -10,7 +10,7 @@ from oracle import oracle as orc
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("variant", [1, 2, 3, 4, 5])
+@pytest.mark.parametrize("variant", [1, 2, 3, 5])
 @pytest.mark.parametrize("s,hq,hkv,causal,dtype", [
     (517, 8, 2, True, torch.bfloat16),    # even GQA group: two heads per CTA, ragged tail
     (390, 6, 2, True, torch.float16),     # odd group size: two query blocks of one head per CTA
@@ -43,7 +43,7 @@ def test_many_items_per_persistent_cta():
 
 def test_d128_only_variants_reject_d256():
     xs = [x.cuda() for x in kf.make_inputs(1, 64, 2, 1, 256, seed=1)]
-    for variant in (3, 4, 5):
+    for variant in (3, 5):
         with pytest.raises(ValueError):
             kf.optimized_attention(*xs, causal=True, variant=variant)
 
