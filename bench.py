@@ -289,7 +289,12 @@ def main():
 
     # ---- timed region: K steps, device time of the operator only (flush excluded).  The operator call makes
     # its two launches back to back (the attention kernel dependent on the prepare), so it is timed as a whole.
+    # Each timed step is followed by a "split" step - the same two launches with an event between them - whose
+    # only purpose is the per-kernel time of the rooflines; interleaving keeps both under the same clock and
+    # power conditions (taken afterwards, the split steps ran 5 % slower: the GPU leaves its burst clocks
+    # within tens of milliseconds).  `ms_per_step` and `value` come from the K operator calls alone.
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(args.steps)]
+    ev2 = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
     barrier()
     if sampler:
         sampler.mark_begin()
@@ -299,6 +304,10 @@ def main():
         ev[i][0].record()
         op()
         ev[i][1].record()
+        flush.zero_()
+        ev2[i][0].record()
+        op_split(ev2[i][1])
+        ev2[i][2].record()
     barrier()
     wall = time.perf_counter() - wall0
     if sampler:
@@ -306,17 +315,8 @@ def main():
     clocks = sampler.stop() if sampler else None
     kf.check_status(dev)
     t_step = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
-    # per-kernel times for the rooflines: the same two launches with an event between them (K more steps)
-    n_split = args.steps
-    ev2 = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(n_split)]
-    for i in range(n_split):
-        flush.zero_()
-        ev2[i][0].record()
-        op_split(ev2[i][1])
-        ev2[i][2].record()
-    torch.cuda.synchronize()
-    t_prep = sum(e[0].elapsed_time(e[1]) for e in ev2) / n_split
-    t_attn = sum(e[1].elapsed_time(e[2]) for e in ev2) / n_split
+    t_prep = sum(e[0].elapsed_time(e[1]) for e in ev2) / args.steps
+    t_attn = sum(e[1].elapsed_time(e[2]) for e in ev2) / args.steps
     times = torch.tensor([t_step, t_prep, t_attn], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
@@ -443,7 +443,7 @@ def main():
                     "breakdown_ms": {"h2d_alone": t_h2d, "d2h_alone": t_d2h, "kernels": t_step,
                                      "note": "slowest rank; each direction copied by itself, all ranks at once"},
                     "h2d_gbs_per_rank": h2d / (t_h2d * 1e-3) / 1e9, "d2h_gbs_per_rank": d2h / (t_d2h * 1e-3) / 1e9},
-            "gpu_launches": 2 * args.steps,  # row-prepare + attention per timed step
+            "gpu_launches": 4 * args.steps,  # row-prepare + attention per timed step, and per interleaved split step
             "clocks": clocks,
             "wall_s_timed_region": wall,
         }

@@ -40,7 +40,9 @@ struct AttnArgs {
     int sg_groups; // (batch, KV head) groups per super-group of the CTA order (see sg_decode)
     int sg_first;  // leading groups that run one after the other
     int* status;  // device status word: 0 = ok, else first failure code
-    unsigned int* sched;  // persistent kernel: {next work item, CTAs that have left}; both 0 between launches
+    unsigned int* sched;  // persistent kernels: {next work item, CTAs that have left}; both 0 between launches
+    void* out;            // output tensor and its element strides, for the kernel that stores rows itself
+    long long o_sb, o_sh, o_ss;
 };
 
 enum : int {

@@ -42,8 +42,8 @@ enum : int {
 // 256 / 128 / 128 threads, must not exceed the 64 K registers of the SM).
 #ifndef KF_PS_REG_SOFTMAX
 #define KF_PS_REG_SOFTMAX 168
-#define KF_PS_REG_AUX 80
-#define KF_PS_REG_CTRL 96
+#define KF_PS_REG_AUX 112
+#define KF_PS_REG_CTRL 64
 #endif
 static_assert(KF_PS_REG_SOFTMAX * 256 + KF_PS_REG_AUX * 128 + KF_PS_REG_CTRL * 128 <= 128 * 512,
               "register re-balance must fit the launch allocation (asking for more blocks forever)");
@@ -432,28 +432,26 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                 uint8_t* tile_smem = smem_q + slot * kPsQSlotBytes + t * kWsTileBytes;
                 uint8_t* orow = tile_smem + gtid * 128;
                 const int sw = gtid & 7;
+                // The whole row is converted into registers first (128 16-bit values = 64 registers) so that the
+                // TMEM columns are released after four loads; the shared-memory staging follows.
+                uint32_t packed[D / 2];
 #pragma unroll
                 for (int q4 = 0; q4 < D / 32; ++q4) {
                     uint32_t o[32];
                     tmem_ld32(lane_base + 256 + t * 128 + q4 * 32, o);
                     tmem_wait_ld();
-                    if (q4 == D / 32 - 1) {
-                        // the output (and the row sums) of this item have been read: its successor may overwrite them
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(c->o_free + t);
-                    }
 #pragma unroll
-                    for (int gq = 0; gq < 4; ++gq) {
-                        uint4 v4;
-                        v4.x = Num<T>::pack(__uint_as_float(o[gq * 8 + 0]) * inv_den, __uint_as_float(o[gq * 8 + 1]) * inv_den);
-                        v4.y = Num<T>::pack(__uint_as_float(o[gq * 8 + 2]) * inv_den, __uint_as_float(o[gq * 8 + 3]) * inv_den);
-                        v4.z = Num<T>::pack(__uint_as_float(o[gq * 8 + 4]) * inv_den, __uint_as_float(o[gq * 8 + 5]) * inv_den);
-                        v4.w = Num<T>::pack(__uint_as_float(o[gq * 8 + 6]) * inv_den, __uint_as_float(o[gq * 8 + 7]) * inv_den);
-                        const int col = q4 * 32 + gq * 8;
-                        *reinterpret_cast<uint4*>(orow + (col / 64) * kBoxBytes + ((((col % 64) / 8) ^ sw) << 4)) = v4;
-                    }
+                    for (int i = 0; i < 16; ++i)
+                        packed[q4 * 16 + i] = Num<T>::pack(__uint_as_float(o[2 * i]) * inv_den, __uint_as_float(o[2 * i + 1]) * inv_den);
                 }
+                // the output (and the row sums) of this item have been read: its successor may overwrite them
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(c->o_free + t);
+#pragma unroll
+                for (int ch = 0; ch < D / 8; ++ch)
+                    *reinterpret_cast<uint4*>(orow + (ch / 8) * kBoxBytes + (((ch % 8) ^ sw) << 4)) =
+                        make_uint4(packed[ch * 4 + 0], packed[ch * 4 + 1], packed[ch * 4 + 2], packed[ch * 4 + 3]);
                 fence_proxy_async_smem();
                 named_barrier_sync(1, 128);
                 if (gtid == 0) {

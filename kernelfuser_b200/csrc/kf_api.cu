@@ -14,6 +14,7 @@
 #include "attn_fwd_basic.cuh"
 #include "attn_fwd_ws.cuh"
 #include "attn_fwd_persist.cuh"
+#include "attn_fwd_persist256.cuh"
 #include "attn_fwd_ws256.cuh"
 #include "prepare_rows.cuh"
 
@@ -215,6 +216,9 @@ constexpr long long kSuperGroupBytes = 48LL << 20;
 // Launches of up to this many CTAs per resident slot interleave their groups.
 constexpr long long kInterleaveMaxCtasPerSlot = 10;
 
+// Sub-blocks of work per SM from which variant 0 picks the persistent kernel at D = 256.
+constexpr long long kPersist256MinSubBlocksPerSm = 200;
+
 // Largest number of 128-row query tiles for which variant 0 picks the one-tile-per-CTA kernel at D = 128.
 constexpr long long kAutoOneTileMaxTiles = 8192;
 
@@ -268,6 +272,23 @@ int launch_attn_persist(const CUtensorMap& mq, const CUtensorMap& mk, const CUte
     const int grid = (int)(items < sm_count() ? items : sm_count());
     e = launch_kernel(kern, dim3((unsigned)grid), dim3(kf::kPsThreads), (size_t)kf::kPsSmemBytes, st, mq, mk, mv, mo, a,
                       (int)items);
+    if (e != cudaSuccess) return fail(KF_ECUDA, "attention launch failed: %s", cudaGetErrorString(e));
+    return KF_OK;
+}
+
+template <typename T>
+int launch_attn_persist256(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const kf::AttnArgs& a0,
+                           cudaStream_t st) {
+    auto kern = kf::attn_fwd_persist256_kernel<T>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kf::kP2SmemBytes);
+    if (e != cudaSuccess) return fail(KF_ECUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
+    kf::AttnArgs a = a0;
+    if (int r = sched_slot(&a.sched)) return r;
+    const long long n_mblk = (a.S + kf::kBM - 1) / kf::kBM;
+    const long long items = n_mblk * a.B * a.Hq;
+    if (items > 0x7fffffffLL) return fail(KF_EINVAL, "too many tiles");
+    const int grid = (int)(items < sm_count() ? items : sm_count());
+    e = launch_kernel(kern, dim3((unsigned)grid), dim3(kf::kP2Threads), (size_t)kf::kP2SmemBytes, st, mq, mk, mv, a, (int)items);
     if (e != cudaSuccess) return fail(KF_ECUDA, "attention launch failed: %s", cudaGetErrorString(e));
     return KF_OK;
 }
@@ -346,6 +367,7 @@ int attention_impl(const void* q, const void* kn, const void* v, const void* gam
     a.eps = eps; a.causal = causal != 0; a.rope = cos_table != nullptr; a.hf_norm = hf_norm != 0;
     a.fuse_q = fuse_q != 0; a.status = status;
     a.factored = factored != 0;
+    a.out = out; a.o_sb = o_sb; a.o_sh = o_sh; a.o_ss = o_ss;
     if (factored && (cos_table || sin_table)) return fail(KF_EINVAL, "the factored form has no rotary tables");
     if (factored && variant != 0 && variant != 2 && variant != 5)
         return fail(KF_EINVAL, "the factored form runs on kernels 0, 2 and 5 only");
@@ -417,6 +439,23 @@ int attention_impl(const void* q, const void* kn, const void* v, const void* gam
         return dtype == KF_BF16 ? launch_attn_ws<__nv_bfloat16>(mq, mk, mv, mo, a, st)
                                 : launch_attn_ws<__half>(mq, mk, mv, mo, a, st);
     }
+    if (D == 256 && variant == 0 && !factored) {
+        // The persistent kernel hides a tile's fixed costs (raw Q copy, transform, copy into TMEM, output store)
+        // behind the previous / next tile's main loop; it pays once every SM has a few hundred 64-key sub-blocks
+        // to work through (measured: -11 % time on C5, -2 ... -6 % on its 8/4-GPU shards, +4 ... +18 % on launches
+        // with about a hundred sub-blocks per SM, where the one-launch-per-tile kernel balances better).
+        const long long n_mblk = (S + kf::kBM - 1) / kf::kBM, n_sub_all = (S + kf::kSub - 1) / kf::kSub;
+        const long long per_head = causal ? n_mblk * (n_mblk + 1) : n_mblk * n_sub_all;
+        if ((long long)B * Hq * per_head >= kPersist256MinSubBlocksPerSm * sm_count()) variant = 3;
+    }
+    if (D == 256 && variant == 3) {
+        if (factored) return fail(KF_EINVAL, "the factored form runs on kernels 0, 2 and 5 only");
+        CUtensorMap mk64, mv64;  // K/V stream in 64-row tiles
+        if (int r = make_map(&mk64, kn, dtype, B, Hkv, S, D, k_sb, k_sh, k_ss, 64)) return r;
+        if (int r = make_map(&mv64, v, dtype, B, Hkv, S, D, v_sb, v_sh, v_ss, 64)) return r;
+        return dtype == KF_BF16 ? launch_attn_persist256<__nv_bfloat16>(mq, mk64, mv64, a, st)
+                                : launch_attn_persist256<__half>(mq, mk64, mv64, a, st);
+    }
     if (D == 256 && (variant == 0 || variant == 2)) {
         CUtensorMap mk64, mv64;  // K/V stream in 64-row tiles
         if (int r = make_map(&mk64, kn, dtype, B, Hkv, S, D, k_sb, k_sh, k_ss, 64)) return r;
@@ -427,7 +466,7 @@ int attention_impl(const void* q, const void* kn, const void* v, const void* gam
         return dtype == KF_BF16 ? launch_attn_ws1<256, __nv_bfloat16>(mq, mk64, mv64, mo, a, st)
                                 : launch_attn_ws1<256, __half>(mq, mk64, mv64, mo, a, st);
     }
-    if (variant >= 2) return fail(KF_EINVAL, "variants 3 and 5 support head dim 128 only");  // D == 256 here
+    if (variant >= 2) return fail(KF_EINVAL, "variant 5 supports head dim 128 only");  // D == 256 here
     if (D == 128)
         return dtype == KF_BF16 ? launch_attn_basic<128, __nv_bfloat16>(mq, mk, mv, mo, a, st)
                                 : launch_attn_basic<128, __half>(mq, mk, mv, mo, a, st);
