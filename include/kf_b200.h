@@ -75,15 +75,19 @@ int kf_prepare_rows(const void* x, void* y, const void* gamma, const void* cos_t
  * fuse_q = 0: q is already prepared (mode 'unfused').
  * kn is the prepared K from kf_prepare_rows; v is the raw V.
  * scale is the softmax scale (the reference passes D^-0.5).
- * variant: 0 = choose automatically (D = 256: kernel 2; D = 128: kernel 5 when
- * B*Hq*ceil(S/128) <= 8192 query tiles, else kernel 2),
+ * variant: 0 = choose automatically.  D = 128: kernel 5 when
+ * B*Hq*ceil(S/128) <= 8192 query tiles, else kernel 3 (kernel 2 for the
+ * factored form).  D = 256: kernel 3 when the launch holds at least 200
+ * sub-blocks of 64 keys per SM, else kernel 2.
  * 1 = baseline kernel (softmax and MMA serialised inside a CTA; any head dim),
- * 2 = pipelined, warp-specialised kernel (D = 128: two Q tiles per CTA;
- * D = 256: one), 3 = persistent pipelined kernel (D = 128), 4 = pipelined
- * kernel that advances in blocks of 128 keys (D = 128), 5 = the one-tile-per-CTA
- * pipelined kernel of D = 256 instantiated for D = 128 with two CTAs per SM.
- * 3 and 4 are measured alternatives; 5 is faster than 2 on small problems and
- * slower on large ones. */
+ * 2 = pipelined, warp-specialised kernel, one launch per work item (D = 128:
+ * two Q tiles per CTA; D = 256: one),
+ * 3 = persistent form of kernel 2: one CTA per SM takes work items from a
+ * device counter and prepares the next item's Q while the running one
+ * computes (D = 128 and D = 256; same results as kernel 2 bit for bit),
+ * 5 = the one-tile-per-CTA kernel of D = 256 instantiated for D = 128 with
+ * two CTAs per SM: faster than 2 and 3 on small problems, slower on large
+ * ones.  4 is not used. */
 int kf_attention_fwd(const void* q, const void* kn, const void* v, const void* gamma_q,
                      const void* cos_table, const void* sin_table, void* out,
                      int B, int Hq, int Hkv, int S, int D, int dtype,

@@ -241,18 +241,20 @@ constexpr int kSchedSlots = 64;
 __device__ unsigned int g_sched[kSchedSlots][2];
 
 int sched_slot(unsigned int** out) {
-    static unsigned int* base[64];
+    static std::atomic<unsigned int*> base[64];
     static std::atomic<unsigned int> turn{0};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(KF_ECUDA, "cudaGetDevice failed");
-    if (base[dev] == nullptr) {
+    unsigned int* bp = base[dev].load(std::memory_order_acquire);
+    if (bp == nullptr) {
         void* p = nullptr;
         cudaError_t e = cudaGetSymbolAddress(&p, g_sched);
         if (e != cudaSuccess || p == nullptr)
             return fail(KF_ECUDA, "cudaGetSymbolAddress(work counters) failed: %s", cudaGetErrorString(e));
-        base[dev] = static_cast<unsigned int*>(p);
+        bp = static_cast<unsigned int*>(p);
+        base[dev].store(bp, std::memory_order_release);
     }
-    *out = base[dev] + 2 * (turn.fetch_add(1, std::memory_order_relaxed) % kSchedSlots);
+    *out = bp + 2 * (turn.fetch_add(1, std::memory_order_relaxed) % kSchedSlots);
     return KF_OK;
 }
 
@@ -589,22 +591,20 @@ namespace {
 // The array's name is only a host-side handle; kernels need its device address,
 // which differs per device and is looked up once per device (with that device
 // current) through cudaGetSymbolAddress.
-void* g_scratch_addr[64];
-bool g_scratch_ready[64];
+std::atomic<void*> g_scratch_addr[64];  // (atomic: two host threads may make a device's first call at once)
 
 int static_scratch_for_current_device(void** out) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return fail(KF_ECUDA, "cudaGetDevice failed");
     if (dev < 0 || dev >= 64) return fail(KF_ECUDA, "device ordinal %d out of range", dev);
-    if (!g_scratch_ready[dev]) {
-        void* p = nullptr;
+    void* p = g_scratch_addr[dev].load(std::memory_order_acquire);
+    if (p == nullptr) {
         cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
         if (e != cudaSuccess || p == nullptr)
             return fail(KF_ECUDA, "cudaGetSymbolAddress(static scratch) failed: %s", cudaGetErrorString(e));
-        g_scratch_addr[dev] = p;
-        g_scratch_ready[dev] = true;
+        g_scratch_addr[dev].store(p, std::memory_order_release);  // (a concurrent first call stores the same address)
     }
-    *out = g_scratch_addr[dev];
+    *out = p;
     return KF_OK;
 }
 }  // namespace
