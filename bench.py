@@ -41,8 +41,10 @@ DTYPE_NAME = {torch.bfloat16: "bf16", torch.float16: "fp16", torch.float32: "fp3
 # workload, from a one-launch ncu capture of this program (three metrics, --clock-control none); keyed by
 # (workload name, kernel).  None where no full-size capture has been taken.
 NCU_DRAM_BYTES_FULL = {
-    ("C4", "attention"): 807741952 + 504647168,   # read + write; algorithmic bytes 1 342 177 280
-    ("C4", "prepare"): 136419840 + 76488960,      # algorithmic bytes 268 435 456 (part of the output is still in L2)
+    ("C4", "attention"): 808484864 + 505497088,    # read + write; algorithmic bytes 1 342 177 280
+    ("C4", "prepare"): 136419840 + 76488960,       # algorithmic bytes 268 435 456 (part of the output is still in L2)
+    ("C5", "attention"): 1102489344 + 509574400,   # algorithmic bytes 1 610 612 736
+    ("C5", "prepare"): 283977472 + 210954240,      # algorithmic bytes 536 870 912
 }
 
 
