@@ -114,6 +114,23 @@ int kf_optimized_attention(const void* q, const void* k, const void* v, const vo
                            int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s,
                            int* status, int variant, void* stream);
 
+/* Full fusion in ONE launch, no prepared-K tensor: k is the RAW key tensor and
+ * the kernel applies RMSNorm/gamma_k/RoPE to every K tile after it lands, as well
+ * as the Q transform in its prologue.  Replaces `launch_attention(mode='full')`
+ * (src/e1_rope_publication_v1.py:667-677; `FUSE_K`, :633-634).  The reference
+ * keeps this form as an ablation (every query tile repeats the K transform) and
+ * so does this library: it runs on the baseline kernel (variant 1) only.  Results
+ * equal kf_prepare_rows + kf_attention_fwd(variant 1) bit for bit. */
+int kf_attention_full(const void* q, const void* k, const void* v, const void* gamma_q, const void* gamma_k,
+                      const void* cos_table, const void* sin_table, void* out,
+                      int B, int Hq, int Hkv, int S, int D, int dtype,
+                      int causal, int hf_norm, float eps, float scale,
+                      int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
+                      int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_s,
+                      int64_t v_stride_b, int64_t v_stride_h, int64_t v_stride_s,
+                      int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s,
+                      int* status, void* stream);
+
 /* Factored no-RoPE form of the operator, both launches in one call.  Replaces
  * `launch_factored_attention` (src/e1_qk_publication_v3.py:638-650:
  * `prepare_factored_kernel` :593-611 + `factored_attention_kernel` :614-635).

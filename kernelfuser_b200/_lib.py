@@ -17,7 +17,7 @@ LIB_PATH = PKG / "libkf_b200.so"
 KF_BF16, KF_FP16 = 0, 1
 EXPORTS = ("kf_version", "kf_last_error", "kf_prepare_rows", "kf_attention_fwd",
            "kf_static_scratch_bytes", "kf_optimized_attention_static", "kf_factored_attention",
-           "kf_selftest_wait_timeout", "kf_optimized_attention")
+           "kf_selftest_wait_timeout", "kf_optimized_attention", "kf_attention_full")
 
 _lib = None
 
@@ -44,6 +44,9 @@ def _declare(lib):
     lib.kf_factored_attention.restype = c_int
     lib.kf_factored_attention.argtypes = ([c_void_p] * 7 + [c_int] * 7 + [c_float] * 2 + [c_int64] * 15 +
                                           [c_void_p, c_int, c_void_p])
+    lib.kf_attention_full.restype = c_int
+    lib.kf_attention_full.argtypes = ([c_void_p] * 8 + [c_int] * 8 + [c_float] * 2 + [c_int64] * 12 +
+                                      [c_void_p, c_void_p])
     lib.kf_optimized_attention.restype = c_int
     lib.kf_optimized_attention.argtypes = ([c_void_p] * 9 + [c_int] * 8 + [c_float] * 2 + [c_int64] * 15 +
                                            [c_void_p, c_int, c_void_p])

@@ -207,6 +207,50 @@ def optimized_attention(q, k, v, gq, gk, cos=None, sin=None, *, causal=False,
     return out
 
 
+def attention_full(q, k, v, gq, gk, cos, sin, out, *, causal, norm_style="hf", eps=1e-6, scale=None):
+    """One launch on the RAW q and k: the kernel transforms every K tile in its loop (see kf_attention_full)."""
+    lib = _lib.load()
+    b, hq, s, d = q.shape
+    sc = float(d ** -0.5 if scale is None else scale)
+    with torch.cuda.device(q.device):
+        _call(lib.kf_attention_full(_ptr(q), _ptr(k), _ptr(v), _ptr(gq), _ptr(gk), _ptr(cos), _ptr(sin), _ptr(out),
+                                    b, hq, k.shape[1], s, d, _DTYPES[q.dtype], int(bool(causal)),
+                                    int(norm_style == "hf"), float(eps), sc,
+                                    *_strides3(q), *_strides3(k), *_strides3(v), *_strides3(out),
+                                    status_word(q.device).data_ptr(), torch.cuda.current_stream().cuda_stream))
+    return out
+
+
+def launch_attention(inputs, out, *, causal=False, mode="query", bm=64, bn=64, warps=4, stages=1, gather=True,
+                     rope=True, hf_norm=True, qn=None, kn=None):
+    """The reference's launcher (src/e1_rope_publication_v1.py:661-677) with its signature and errors: full fusion
+    (``mode='full'``: one launch, K transformed per tile, no scratch), query-only fusion (``'query'``: K prepared
+    into ``kn``, Q transformed in the attention prologue) or the two-kernel unfused control (``'unfused'``: Q into
+    ``qn`` and K into ``kn`` first).  ``inputs`` = ``(q, k, v, gq, gk, cos, sin)``; ``rope=False`` ignores the tables;
+    ``bm``, ``bn``, ``warps``, ``stages`` and ``gather`` tune the Triton kernels there and do not change the
+    result, so they are accepted and ignored.  Like the reference's launcher it checks the mode and the scratch
+    buffers only (plus: the tensors must be on a GPU); shapes and dtypes are what ``optimized_attention`` checks."""
+    if mode not in ("full", "query", "unfused"):
+        raise ValueError("Invalid fusion mode")
+    q, k, v, gq, gk, cos, sin = inputs
+    if not rope:
+        cos = sin = None
+    if not all(t.is_cuda for t in (q, k, v, gq, gk, out)):
+        raise ValueError("Expected CUDA tensors")  # there is no CPU path
+    if mode == "full":
+        _check_strided(q, k, v)
+    style = "hf" if hf_norm else "legacy"
+    if mode == "full":
+        return attention_full(q, k, v, gq, gk, cos, sin, out, causal=causal, norm_style=style)
+    if kn is None or (mode == "unfused" and qn is None):
+        raise ValueError("Missing scratch buffers")
+    prepare_rows(k, gk, cos, sin, norm_style=style, out=kn)
+    if mode == "unfused":
+        prepare_rows(q, gq, cos, sin, norm_style=style, out=qn)
+        return attention_forward(qn, kn, v, gq, cos, sin, out, causal=causal, norm_style=style, fuse_q=False)
+    return attention_forward(q, kn, v, gq, cos, sin, out, causal=causal, norm_style=style, fuse_q=True)
+
+
 def fused(q, k, v, gq, gk, cos, sin, causal, eps=1e-6, scale=None, norm_style="qwen3", *, out_layout="bhsd"):
     """Runner-arm adapter with the signature of the reference's arms
     (``fused``/``separate``/``vendor``/``compiled_fn``,

@@ -30,12 +30,14 @@ namespace kf {
 
 struct AttnArgs {
     const void* gq;   // [D] gamma for the Q prologue
+    const void* gk;   // [D] gamma for K tiles transformed inside the loop (fuse_k), else unused
     const void* cos;  // [S, D] or null
     const void* sin;  // [S, D] or null
     int B, Hq, Hkv, S;
     float scale_log2e;  // softmax scale * log2(e)
     float eps;
     int causal, rope, hf_norm, fuse_q;
+    int fuse_k;    // the K operand is the RAW key tensor: every tile is normalised and rotated after it lands
     int factored;  // factored no-RoPE form: q stays raw, scores are scaled by the row's inverse RMS
     int sg_groups; // (batch, KV head) groups per super-group of the CTA order (see sg_decode)
     int sg_first;  // leading groups that run one after the other
@@ -69,8 +71,11 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // table reads; the table chunks of the first batch of rows are fetched
 // BEFORE `wait_q()` (which blocks until the raw tile has landed), so their
 // latency overlaps the Q copy.  Returns false if the wait failed.
+// `gamma` is the weight of the rows in the tile (Q's, or K's when a key tile is transformed in the loop) and
+// `m0` the sequence position of its first row.
 template <int D, typename T, int HALVES = 2, int WARPS = 4, typename WaitFn>
-__device__ __forceinline__ bool q_prologue_coop(uint8_t* smem_q, int gtid, int m0, const AttnArgs& a, WaitFn&& wait_q) {
+__device__ __forceinline__ bool rows_prologue_coop(uint8_t* smem_q, int gtid, int m0, const AttnArgs& a, const void* gamma,
+                                                   WaitFn&& wait_q) {
     constexpr int LPR = D / 16;              // lanes per row
     constexpr int RPW = 32 / LPR;            // rows per warp step
     constexpr int NIT = kBM / (WARPS * RPW);     // steps
@@ -79,7 +84,7 @@ __device__ __forceinline__ bool q_prologue_coop(uint8_t* smem_q, int gtid, int m
     const int lane = gtid & 31, w = gtid >> 5;
     const int sub = lane % LPR, rsub = lane / LPR;
     const bool hf = a.hf_norm != 0;
-    const uint4* g4 = reinterpret_cast<const uint4*>(a.gq);
+    const uint4* g4 = reinterpret_cast<const uint4*>(gamma);
     const uint4 glo = __ldg(g4 + sub), ghi = __ldg(g4 + LPR + sub);
     uint4 tb[HALF][4];
     auto load_tables = [&](int it0) {
@@ -122,6 +127,11 @@ __device__ __forceinline__ bool q_prologue_coop(uint8_t* smem_q, int gtid, int m
         }
     }
     return true;
+}
+
+template <int D, typename T, int HALVES = 2, int WARPS = 4, typename WaitFn>
+__device__ __forceinline__ bool q_prologue_coop(uint8_t* smem_q, int gtid, int m0, const AttnArgs& a, WaitFn&& wait_q) {
+    return rows_prologue_coop<D, T, HALVES, WARPS>(smem_q, gtid, m0, a, a.gq, static_cast<WaitFn&&>(wait_q));
 }
 
 // CTA order of the pipelined kernels.  The (batch, KV head) groups are cut into super-groups of
@@ -297,6 +307,14 @@ attn_fwd_basic_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     for (int j = 0; j < nblk && !fail; ++j) {
         const uint32_t ph = j & 1;
         const int n0 = j * kBN;
+        if (a.fuse_k) {
+            // The reference's full fusion (`FUSE_K`, src/e1_rope_publication_v1.py:633-634): the tile that landed
+            // is the raw K; all threads normalise and rotate it in place (positions n0 ...) before the MMA reads it.
+            auto wait_k = [&]() { return __all_sync(0xffffffffu, mbar_wait(bar_k, ph)) != 0; };
+            const bool ok = rows_prologue_coop<D, T, 4>(smem_k, tid, n0, a, a.gk, wait_k);
+            if (ok) fence_proxy_async_smem();
+            if (__syncthreads_or(!ok)) { fail = kStatusWaitK; break; }
+        }
         // ---------------- S = Q K^T
         if (warp == 0 && elect_one()) {
             if (!mbar_wait(bar_k, ph)) {
@@ -314,8 +332,8 @@ attn_fwd_basic_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             }
         }
         __syncwarp();
-        if (fail) break;
-        if (!mbar_wait(bar_s, ph)) { fail = kStatusWaitS; break; }
+        // (the CTA follows one outcome: a thread that left here alone would miss the barriers below)
+        if (__syncthreads_or(fail != 0 || !mbar_wait(bar_s, ph))) { if (!fail) fail = kStatusWaitS; break; }
         tc_fence_after();
         if (warp == 0 && j + 1 < nblk && elect_one()) {  // K buffer is free again
             mbar_expect_tx(bar_k, kTileBytes);
@@ -396,8 +414,7 @@ attn_fwd_basic_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             }
         }
         __syncwarp();
-        if (fail) break;
-        if (!mbar_wait(bar_o, ph)) { fail = kStatusWaitO; break; }
+        if (__syncthreads_or(fail != 0 || !mbar_wait(bar_o, ph))) { if (!fail) fail = kStatusWaitO; break; }
         tc_fence_after();
         if (warp == 0 && j + 1 < nblk && elect_one()) {  // V buffer (and S/P columns) are free again
             mbar_expect_tx(bar_v, kTileBytes);

@@ -336,7 +336,10 @@ int attention_impl(const void* q, const void* kn, const void* v, const void* gam
                      const void* sin_table, void* out, int B, int Hq, int Hkv, int S, int D, int dtype, int causal,
                      int hf_norm, int fuse_q, float eps, float scale, int64_t q_sb, int64_t q_sh, int64_t q_ss,
                      int64_t k_sb, int64_t k_sh, int64_t k_ss, int64_t v_sb, int64_t v_sh, int64_t v_ss,
-                     int64_t o_sb, int64_t o_sh, int64_t o_ss, int* status, int variant, int factored, void* stream) {
+                     int64_t o_sb, int64_t o_sh, int64_t o_ss, int* status, int variant, int factored, void* stream,
+                     const void* gamma_k_full = nullptr) {
+    // gamma_k_full != NULL: `kn` is the RAW key tensor and every K tile is normalised and rotated inside the loop
+    // (the reference's mode 'full'); that form exists in the baseline kernel only.
     if (int r = check_common(B, Hq, S, D, dtype)) return r;
     if (Hkv < 1 || Hq % Hkv != 0) return fail(KF_EINVAL, "Hq (%d) must be a positive multiple of Hkv (%d)", Hq, Hkv);
     if (!q || !kn || !v || !out || !status) return fail(KF_EINVAL, "q, kn, v, out and status must not be NULL");
@@ -354,6 +357,11 @@ int attention_impl(const void* q, const void* kn, const void* v, const void* gam
     if (q_ss < D || k_ss < D || v_ss < D || o_ss < D) return fail(KF_EINVAL, "row stride must be at least D");
     if (!(scale > 0.f) || !(scale < 1e30f)) return fail(KF_EINVAL, "scale must be positive and finite");
     if (variant < 0 || variant > 5 || variant == 4) return fail(KF_EINVAL, "variant must be 0, 1, 2, 3 or 5");
+    if (gamma_k_full) {
+        if (!aligned16(gamma_k_full)) return fail(KF_EALIGN, "pointers must be 16-byte aligned");
+        if (!fuse_q || factored) return fail(KF_EINVAL, "full fusion transforms both Q and K in the kernel");
+        variant = 1;
+    }
     if (int r = check_device()) return r;
 
     CUtensorMap mq, mk, mv, mo;
@@ -368,6 +376,7 @@ int attention_impl(const void* q, const void* kn, const void* v, const void* gam
     a.scale_log2e = scale * 1.4426950408889634f;
     a.eps = eps; a.causal = causal != 0; a.rope = cos_table != nullptr; a.hf_norm = hf_norm != 0;
     a.fuse_q = fuse_q != 0; a.status = status;
+    a.gk = gamma_k_full; a.fuse_k = gamma_k_full != nullptr;
     a.factored = factored != 0;
     a.out = out; a.o_sb = o_sb; a.o_sh = o_sh; a.o_ss = o_ss;
     if (factored && (cos_table || sin_table)) return fail(KF_EINVAL, "the factored form has no rotary tables");
@@ -549,6 +558,22 @@ int kf_optimized_attention(const void* q, const void* k, const void* v, const vo
     return attention_impl(q, kn, v, gamma_q, cos_table, sin_table, out, B, Hq, Hkv, S, D, dtype, causal, hf_norm,
                                  /*fuse_q=*/1, eps, scale, q_sb, q_sh, q_ss, n_sb, n_sh, n_ss, v_sb, v_sh, v_ss, o_sb,
                                  o_sh, o_ss, status, variant, /*factored=*/0, stream);
+}
+
+// Full fusion: one launch, no prepared-K tensor; the kernel normalises and rotates every K tile after it lands
+// (the reference's `launch_attention(mode='full')`, src/e1_rope_publication_v1.py:667-677 with FUSE_K :633-634).
+// The reference keeps this form as an ablation - every query tile repeats the K transform - and so does this
+// library: it runs on the baseline kernel only.  Results equal those of kf_optimized_attention with variant 1
+// bit for bit (same rounding points, same loop).
+int kf_attention_full(const void* q, const void* k, const void* v, const void* gamma_q, const void* gamma_k,
+                      const void* cos_table, const void* sin_table, void* out, int B, int Hq, int Hkv, int S, int D,
+                      int dtype, int causal, int hf_norm, float eps, float scale, int64_t q_sb, int64_t q_sh,
+                      int64_t q_ss, int64_t k_sb, int64_t k_sh, int64_t k_ss, int64_t v_sb, int64_t v_sh, int64_t v_ss,
+                      int64_t o_sb, int64_t o_sh, int64_t o_ss, int* status, void* stream) {
+    if (!gamma_q || !gamma_k) return fail(KF_EINVAL, "gamma_q and gamma_k must not be NULL");
+    return attention_impl(q, k, v, gamma_q, cos_table, sin_table, out, B, Hq, Hkv, S, D, dtype, causal, hf_norm,
+                          /*fuse_q=*/1, eps, scale, q_sb, q_sh, q_ss, k_sb, k_sh, k_ss, v_sb, v_sh, v_ss, o_sb, o_sh,
+                          o_ss, status, /*variant=*/1, /*factored=*/0, stream, gamma_k);
 }
 
 // Factored no-RoPE form of the operator (the reference's `launch_factored_attention`,

@@ -73,6 +73,12 @@ def test_c_abi_rejects_bad_arguments_before_launch():
     assert rc == -1
     rc = lib.kf_selftest_wait_timeout(p, 0, None)
     assert rc == -1
+    # the one-launch form: both weights are required, and the same stride rule holds
+    rc = lib.kf_attention_full(p, p, p, p, None, None, None, p, 1, 4, 2, 8, 128, 0, 1, 1, 1e-6, 0.1, *(st * 4), p, None)
+    assert rc == -1 and b"gamma" in lib.kf_last_error()
+    rc = lib.kf_attention_full(p, p, p, p, p, None, None, p, 2, 4, 2, 8, 128, 0, 1, 1, 1e-6, 0.1,
+                               0, st[1], st[2], *(st * 3), p, None)
+    assert rc == -2 and b"size 1" in lib.kf_last_error()
 
 
 def test_expanded_views_are_refused_by_the_adapters():
@@ -133,6 +139,11 @@ def test_misuse_raises_value_error():
         kf.factored_attention(q, k, v, gq, gk, causal=True)
     with pytest.raises(ValueError, match="Expected Q"):
         kf.factored_attention(q, k[:, :, :5], v, gq, gk)
+    # the reference's launcher: its two errors, and CPU tensors
+    with pytest.raises(ValueError, match="Invalid fusion mode"):
+        kf.launch_attention((q, k, v, gq, gk, cos, sin), torch.empty_like(q), mode="key")
+    with pytest.raises(ValueError, match="CUDA"):
+        kf.launch_attention((q, k, v, gq, gk, cos, sin), torch.empty_like(q), mode="full")
     # the arm adapter: unknown output layout, and CPU tensors
     with pytest.raises(ValueError, match="out_layout"):
         kf.fused(q, k, v, gq, gk, cos, sin, True, out_layout="sbhd")
