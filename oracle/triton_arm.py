@@ -166,7 +166,7 @@ FUSION_SHAPES = [("B1_S128", 1, 128, 32, 8, 128, 1e6), ("B8_S128", 8, 128, 32, 8
                  ("C5", 8, 8192, 16, 8, 256, 1e4)]
 
 
-def fusion_table(ref, kf, paired, path):
+def fusion_table(ref, kf, paired, path, with_full=False):
     rows = []
     for name, b, s, hq, hkv, d, theta in FUSION_SHAPES:
         xs = kf.make_inputs(b, s, hq, hkv, d, dtype=torch.bfloat16, theta=theta, seed=0)
@@ -182,6 +182,11 @@ def fusion_table(ref, kf, paired, path):
             "triton_unfused": lambda: ref.launch_attention(inputs, out, causal=True, mode="unfused", bm=64, bn=128,
                                                            gather=False, qn=qn, kn=kn),
         }
+        if with_full:
+            # full fusion, one launch (the reference's tuned tiling for that mode: BM=32, BN=64, `:834`)
+            fns["cuda_full"] = lambda: kf.launch_attention(inputs, out, causal=True, mode="full")
+            fns["triton_full"] = lambda: ref.launch_attention(inputs, out, causal=True, mode="full", bm=32, bn=64,
+                                                              gather=False)
         big = b * hq * s * s > (1 << 32)
         t = paired(fns, rounds=3, samples=5, replays=5 if big else 20)
         kf.check_status()
@@ -199,6 +204,7 @@ def fusion_table(ref, kf, paired, path):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--fusion-table", default="", help="write the fused-vs-unfused timing table to this JSON file")
+    ap.add_argument("--with-full", action="store_true", help="add the one-launch full-fusion arms to the table")
     ap.add_argument("--golden", default="")
     ap.add_argument("--out", default=str(ROOT / "gpurun_out" / "triton_arm.json"))
     ap.add_argument("--quick", action="store_true")
@@ -213,7 +219,7 @@ def main():
         write_golden(ref, kf, args.golden)
         return
     if args.fusion_table:
-        fusion_table(ref, kf, paired, args.fusion_table)
+        fusion_table(ref, kf, paired, args.fusion_table, with_full=args.with_full)
         return
     want = set(filter(None, args.cases.split(",")))
     recs = []
