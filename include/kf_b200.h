@@ -75,10 +75,11 @@ int kf_prepare_rows(const void* x, void* y, const void* gamma, const void* cos_t
  * fuse_q = 0: q is already prepared (mode 'unfused').
  * kn is the prepared K from kf_prepare_rows; v is the raw V.
  * scale is the softmax scale (the reference passes D^-0.5).
- * variant: 0 = choose automatically.  D = 128: kernel 5 when
- * B*Hq*ceil(S/128) <= 8192 query tiles, else kernel 3 (kernel 2 for the
- * factored form).  D = 256: kernel 3 when the launch holds at least 200
- * sub-blocks of 64 keys per SM, else kernel 2.
+ * variant: 0 = choose automatically.  D = 128: kernel 3 when the launch has
+ * at least 8192 query tiles (B*Hq*ceil(S/128)) and 2048 < S < 8192, else
+ * kernel 5 (factored form: kernel 2 above 8192 tiles, else 5).  D = 256:
+ * kernel 3 when the launch holds at least 200 sub-blocks of 64 keys per SM,
+ * else kernel 2.
  * 1 = baseline kernel (softmax and MMA serialised inside a CTA; any head dim),
  * 2 = pipelined, warp-specialised kernel, one launch per work item (D = 128:
  * two Q tiles per CTA; D = 256: one),

@@ -219,8 +219,10 @@ constexpr long long kInterleaveMaxCtasPerSlot = 10;
 // Sub-blocks of work per SM from which variant 0 picks the persistent kernel at D = 256.
 constexpr long long kPersist256MinSubBlocksPerSm = 200;
 
-// Largest number of 128-row query tiles for which variant 0 picks the one-tile-per-CTA kernel at D = 128.
-constexpr long long kAutoOneTileMaxTiles = 8192;
+// Variant 0 at D = 128 picks the persistent two-tile kernel from this many 128-row query tiles, for sequence
+// lengths strictly between the two limits below, and the one-tile-per-CTA kernel everywhere else.
+constexpr long long kAutoPersistMinTiles = 8192;
+constexpr int kAutoPersistMinS = 2048, kAutoPersistMaxS = 8192;
 
 int sm_count() {
     static int cached[64];
@@ -383,16 +385,18 @@ int attention_impl(const void* q, const void* kn, const void* v, const void* gam
     if (factored && variant != 0 && variant != 2 && variant != 5)
         return fail(KF_EINVAL, "the factored form runs on kernels 0, 2 and 5 only");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    // Automatic choice at D = 128: the one-tile-per-CTA kernel (two CTAs per SM, groups interleaved heaviest
-    // first) fills the SMs and keeps the causal tail short; measured on B200 it is 4-17 % faster than the
-    // two-tiles-per-CTA kernel up to about two thousand query tiles, 1-4 % faster up to about eight thousand
-    // and 2-5 % slower at sixteen thousand (C4), where the shared K/V stream of the tile pair pays.
+    // Automatic choice at D = 128.  The one-tile-per-CTA kernel (two CTAs per SM, groups interleaved heaviest
+    // first) fills the SMs, keeps the causal tail short and has the better steady state (two independent CTAs
+    // instead of two tiles in step): measured on B200 it is 3-9 % faster than the persistent two-tile kernel at
+    // S <= 2048 and S >= 8192 whatever the size of the launch, and 1-17 % faster on launches below about eight
+    // thousand query tiles.  In between (S = 3072 ... 6144 with at least 8192 tiles, C4 and its 2-GPU shard among
+    // them) the persistent kernel wins by 2-6 %: it hides the per-tile fixed costs, which weigh most there, and
+    // its tile pair shares one K/V stream.  (The factored form exists for kernels 2 and 5 only.)
     if (D == 128 && variant == 0) {
         const long long tiles = (long long)B * Hq * ((S + kf::kBM - 1) / kf::kBM);
-        // Above that size two tiles per CTA share a K/V stream; the persistent form of that kernel hides the
-        // per-item fixed costs and measured ~3 % faster than the one-launch-per-item form at sixteen thousand
-        // tiles.  (The factored form exists for kernels 2 and 5 only.)
-        variant = tiles <= kAutoOneTileMaxTiles ? 5 : (factored ? 2 : 3);
+        const bool mid = S > kAutoPersistMinS && S < kAutoPersistMaxS;
+        if (factored) variant = tiles > kAutoPersistMinTiles ? 2 : 5;
+        else variant = (tiles >= kAutoPersistMinTiles && mid) ? 3 : 5;
     }
     if (D == 128 && variant == 3) {
         CUtensorMap mk64, mv64;  // the persistent kernel streams K/V in 64-row tiles
