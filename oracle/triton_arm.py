@@ -16,9 +16,9 @@ For every case it records
   * per-call device time of both by the reference's graph-replay protocol
     (src/fusion_harness.py:32-79).
 
-    python oracle/triton_arm.py [--out gpurun_out/triton_arm.json] [--quick]
-    python oracle/triton_arm.py --golden gpurun_out/triton_arm_b200.npz
-    python oracle/triton_arm.py --fusion-table gpurun_out/fusion_table.json
+    python oracle/triton_arm.py [--out OUT/triton_arm.json] [--quick]
+    python oracle/triton_arm.py --golden OUT/triton_arm_b200.npz
+    python oracle/triton_arm.py --fusion-table OUT/fusion_table.json [--with-full]
 
 The second form writes the fixture ``tests/golden/triton_arm_b200.npz`` is a copy
 of: prepared K and outputs of the real arm on small seeded cases (inputs are
@@ -28,6 +28,7 @@ regenerated from the seed by the tests), which pin ``emulate_rows`` /
 from __future__ import annotations
 
 import argparse
+import tempfile
 import json
 import sys
 from pathlib import Path
@@ -206,7 +207,7 @@ def main():
     ap.add_argument("--fusion-table", default="", help="write the fused-vs-unfused timing table to this JSON file")
     ap.add_argument("--with-full", action="store_true", help="add the one-launch full-fusion arms to the table")
     ap.add_argument("--golden", default="")
-    ap.add_argument("--out", default=str(ROOT / "gpurun_out" / "triton_arm.json"))
+    ap.add_argument("--out", default=str(Path(tempfile.gettempdir()) / "triton_arm.json"))
     ap.add_argument("--quick", action="store_true")
     ap.add_argument("--cases", default="")
     args = ap.parse_args()
