@@ -514,7 +514,7 @@ __global__ void selftest_wait_kernel(int* status, long long limit_clocks) {
 
 extern "C" {
 
-int kf_version(void) { return 101; }
+int kf_version(void) { return 102; }
 
 int kf_selftest_wait_timeout(int* status, long long limit_clocks, void* stream) {
     if (!status) return fail(KF_EINVAL, "status must not be NULL");
