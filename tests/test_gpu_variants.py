@@ -62,3 +62,29 @@ def test_d256_variants_match_oracle(variant, s, hq, hkv, causal, dtype):
     kf.check_status()
     m = orc.metric(out.cpu(), ref)
     assert orc.within_tolerance(m), (variant, s, hq, hkv, m)
+
+
+def test_persistent_kernels_reuse_their_counter_slots():
+    # The persistent kernels take work from counters in the library image, 64 slots used in turn and reset by
+    # the last CTA of each launch: run more launches than slots, on two streams, both head dims, and compare
+    # every result with the first one of its kind.
+    xs128 = [x.cuda() for x in kf.make_inputs(2, 640, 8, 2, 128, seed=5)]
+    xs256 = [x.cuda() for x in kf.make_inputs(1, 512, 4, 2, 256, theta=1e4, seed=6)]
+    ref128 = kf.optimized_attention(*xs128, causal=True, variant=3)
+    ref256 = kf.optimized_attention(*xs256, causal=True, variant=3)
+    torch.cuda.synchronize()
+    kf.check_status()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    outs = []
+    for i in range(100):
+        xs, ref = (xs128, ref128) if i % 3 else (xs256, ref256)
+        if i % 2:
+            with torch.cuda.stream(side):
+                outs.append((kf.optimized_attention(*xs, causal=True, variant=3), ref))
+        else:
+            outs.append((kf.optimized_attention(*xs, causal=True, variant=3), ref))
+    torch.cuda.synchronize()
+    kf.check_status()
+    for out, ref in outs:
+        assert torch.equal(out, ref)
