@@ -314,6 +314,10 @@ attn_fwd_ws1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         if (elect_one()) {
             int s = 0;
             uint32_t epar = 1;  // passes at once on the first turn of the ring
+            // K is the output of the row-prepare launched just before this kernel: when this grid was launched as
+            // its programmatic dependent, everything up to here (barriers, TMEM, the raw Q copy and its transform)
+            // has overlapped the prepare, and the first K copy waits for it to complete.
+            grid_dep_wait();
             for (int jj = 0; jj < n_sub; ++jj) {
                 // (the Q buffer becomes a stage only after the prepared Q has been copied to TMEM)
                 if (kNS > kW256Stages && jj == kW256Stages && !mbar_wait_abortable(q_ready, 0, s_abort)) { fail = kStatusWsQReady; break; }

@@ -39,14 +39,28 @@ int fail(int code, const char* fmt, ...) {
     return code;
 }
 
+// `dependent`: launch as a programmatic dependent of the kernel before it in the stream (the grid may start while
+// that kernel still runs and must order its reads of that kernel's output with griddepcontrol.wait).
 template <typename... KArgs, typename... Args>
-cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+cudaError_t launch_kernel_ex(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool dependent,
+                             Args&&... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    if (dependent) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
     return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
+}
+template <typename... KArgs, typename... Args>
+cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+    return launch_kernel_ex(kern, grid, block, smem, st, false, std::forward<Args>(args)...);
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -198,7 +212,7 @@ int launch_attn_ws(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorM
 
 template <int D, typename T, bool FACTORED = false>
 int launch_attn_ws1(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
-                    const kf::AttnArgs& a, cudaStream_t st) {
+                    const kf::AttnArgs& a, cudaStream_t st, bool dependent = false) {
     auto kern = kf::attn_fwd_ws1_kernel<D, T, FACTORED>;
     constexpr int smem = kf::ws1_smem_bytes<D>(FACTORED);
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -206,7 +220,7 @@ int launch_attn_ws1(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensor
     const long long n_mblk = (a.S + kf::kBM - 1) / kf::kBM;
     const long long grid = n_mblk * a.B * a.Hq;
     if (grid > 0x7fffffffLL) return fail(KF_EINVAL, "too many tiles");
-    e = launch_kernel(kern, dim3((unsigned)grid), dim3(kf::kW256Threads), (size_t)smem, st, mq, mk, mv, mo, a);
+    e = launch_kernel_ex(kern, dim3((unsigned)grid), dim3(kf::kW256Threads), (size_t)smem, st, dependent, mq, mk, mv, mo, a);
     if (e != cudaSuccess) return fail(KF_ECUDA, "attention launch failed: %s", cudaGetErrorString(e));
     return KF_OK;
 }
@@ -215,6 +229,16 @@ int launch_attn_ws1(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensor
 constexpr long long kSuperGroupBytes = 48LL << 20;
 // Launches of up to this many CTAs per resident slot interleave their groups.
 constexpr long long kInterleaveMaxCtasPerSlot = 10;
+
+// The one-tile kernel starts as a programmatic dependent of the row-prepare made by the same call: the prepare's
+// tail and the launch gap then hide behind the attention kernel's own start-up (barriers, TMEM, raw Q copy, Q
+// transform); only its first K copy waits for the prepare (griddepcontrol.wait).  Measured under graph replay:
+// -17 % at B=1 S=128, -10 % at B=1 S=512, -3 % on C2 (B=1 S=2048), -0.7 % on the 8- and 4-GPU shards of C4;
+// identical results.  The limit (in 128-row query tiles) exists for experiments; every launch qualifies.
+#ifndef KF_DEPENDENT_MAX_TILES
+#define KF_DEPENDENT_MAX_TILES (1LL << 40)
+#endif
+constexpr long long kDependentMaxTiles = KF_DEPENDENT_MAX_TILES;
 
 // Sub-blocks of work per SM from which variant 0 picks the persistent kernel at D = 256.
 constexpr long long kPersist256MinSubBlocksPerSm = 200;
@@ -339,7 +363,9 @@ int attention_impl(const void* q, const void* kn, const void* v, const void* gam
                      int hf_norm, int fuse_q, float eps, float scale, int64_t q_sb, int64_t q_sh, int64_t q_ss,
                      int64_t k_sb, int64_t k_sh, int64_t k_ss, int64_t v_sb, int64_t v_sh, int64_t v_ss,
                      int64_t o_sb, int64_t o_sh, int64_t o_ss, int* status, int variant, int factored, void* stream,
-                     const void* gamma_k_full = nullptr) {
+                     const void* gamma_k_full = nullptr, bool after_prepare = false) {
+    // after_prepare: the launch before this one in the stream is the row-prepare that wrote `kn`, made by the same
+    // call; small launches of the one-tile kernel then start as its programmatic dependent.
     // gamma_k_full != NULL: `kn` is the RAW key tensor and every K tile is normalised and rotated inside the loop
     // (the reference's mode 'full'); that form exists in the baseline kernel only.
     if (int r = check_common(B, Hq, S, D, dtype)) return r;
@@ -385,6 +411,7 @@ int attention_impl(const void* q, const void* kn, const void* v, const void* gam
     if (factored && variant != 0 && variant != 2 && variant != 5)
         return fail(KF_EINVAL, "the factored form runs on kernels 0, 2 and 5 only");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool dependent = after_prepare && (long long)B * Hq * ((S + kf::kBM - 1) / kf::kBM) <= kDependentMaxTiles;
     // Automatic choice at D = 128.  The one-tile-per-CTA kernel (two CTAs per SM, groups interleaved heaviest
     // first) fills the SMs, keeps the causal tail short and has the better steady state (two independent CTAs
     // instead of two tiles in step): measured on B200 it is 3-9 % faster than the persistent two-tile kernel at
@@ -442,10 +469,10 @@ int attention_impl(const void* q, const void* kn, const void* v, const void* gam
         if (int r = make_map(&mk64, kn, dtype, B, Hkv, S, D, k_sb, k_sh, k_ss, 64)) return r;
         if (int r = make_map(&mv64, v, dtype, B, Hkv, S, D, v_sb, v_sh, v_ss, 64)) return r;
         if (factored)
-            return dtype == KF_BF16 ? launch_attn_ws1<128, __nv_bfloat16, true>(mq, mk64, mv64, mo, a, st)
-                                    : launch_attn_ws1<128, __half, true>(mq, mk64, mv64, mo, a, st);
-        return dtype == KF_BF16 ? launch_attn_ws1<128, __nv_bfloat16>(mq, mk64, mv64, mo, a, st)
-                                : launch_attn_ws1<128, __half>(mq, mk64, mv64, mo, a, st);
+            return dtype == KF_BF16 ? launch_attn_ws1<128, __nv_bfloat16, true>(mq, mk64, mv64, mo, a, st, dependent)
+                                    : launch_attn_ws1<128, __half, true>(mq, mk64, mv64, mo, a, st, dependent);
+        return dtype == KF_BF16 ? launch_attn_ws1<128, __nv_bfloat16>(mq, mk64, mv64, mo, a, st, dependent)
+                                : launch_attn_ws1<128, __half>(mq, mk64, mv64, mo, a, st, dependent);
     }
     if (D == 128 && variant == 2) {
         if (factored)
@@ -476,10 +503,10 @@ int attention_impl(const void* q, const void* kn, const void* v, const void* gam
         if (int r = make_map(&mk64, kn, dtype, B, Hkv, S, D, k_sb, k_sh, k_ss, 64)) return r;
         if (int r = make_map(&mv64, v, dtype, B, Hkv, S, D, v_sb, v_sh, v_ss, 64)) return r;
         if (factored)
-            return dtype == KF_BF16 ? launch_attn_ws1<256, __nv_bfloat16, true>(mq, mk64, mv64, mo, a, st)
-                                    : launch_attn_ws1<256, __half, true>(mq, mk64, mv64, mo, a, st);
-        return dtype == KF_BF16 ? launch_attn_ws1<256, __nv_bfloat16>(mq, mk64, mv64, mo, a, st)
-                                : launch_attn_ws1<256, __half>(mq, mk64, mv64, mo, a, st);
+            return dtype == KF_BF16 ? launch_attn_ws1<256, __nv_bfloat16, true>(mq, mk64, mv64, mo, a, st, dependent)
+                                    : launch_attn_ws1<256, __half, true>(mq, mk64, mv64, mo, a, st, dependent);
+        return dtype == KF_BF16 ? launch_attn_ws1<256, __nv_bfloat16>(mq, mk64, mv64, mo, a, st, dependent)
+                                : launch_attn_ws1<256, __half>(mq, mk64, mv64, mo, a, st, dependent);
     }
     if (variant >= 2) return fail(KF_EINVAL, "variant 5 supports head dim 128 only");  // D == 256 here
     if (D == 128)
@@ -546,9 +573,8 @@ int kf_attention_fwd(const void* q, const void* kn, const void* v, const void* g
 }
 
 // The whole operator in one call: row-prepare of K into the caller's `kn`, then the attention kernel - the
-// reference's `launch_attention(mode='query')` (src/e1_rope_publication_v1.py:661-677).  (Launching the
-// attention kernel programmatically dependent on the prepare was measured and dropped: its early CTAs compete
-// with the prepare's tail for memory bandwidth and the pair came out 2-3 % slower on the per-GPU shards.)
+// reference's `launch_attention(mode='query')` (src/e1_rope_publication_v1.py:661-677).  Where the one-tile
+// kernel serves the launch it starts as a programmatic dependent of the prepare (see kDependentMaxTiles).
 int kf_optimized_attention(const void* q, const void* k, const void* v, const void* gamma_q, const void* gamma_k,
                            const void* cos_table, const void* sin_table, void* kn, void* out, int B, int Hq, int Hkv,
                            int S, int D, int dtype, int causal, int hf_norm, float eps, float scale, int64_t q_sb,
@@ -561,7 +587,8 @@ int kf_optimized_attention(const void* q, const void* k, const void* v, const vo
         return r;
     return attention_impl(q, kn, v, gamma_q, cos_table, sin_table, out, B, Hq, Hkv, S, D, dtype, causal, hf_norm,
                                  /*fuse_q=*/1, eps, scale, q_sb, q_sh, q_ss, n_sb, n_sh, n_ss, v_sb, v_sh, v_ss, o_sb,
-                                 o_sh, o_ss, status, variant, /*factored=*/0, stream);
+                                 o_sh, o_ss, status, variant, /*factored=*/0, stream, /*gamma_k_full=*/nullptr,
+                                 /*after_prepare=*/true);
 }
 
 // Full fusion: one launch, no prepared-K tensor; the kernel normalises and rotates every K tile after it lands
@@ -596,7 +623,7 @@ int kf_factored_attention(const void* q, const void* k, const void* v, const voi
         return r;
     return attention_impl(q, kn, v, gamma_q, nullptr, nullptr, out, B, Hq, Hkv, S, D, dtype, causal, /*hf_norm=*/0,
                           /*fuse_q=*/1, eps, scale, q_sb, q_sh, q_ss, n_sb, n_sh, n_ss, v_sb, v_sh, v_ss, o_sb, o_sh,
-                          o_ss, status, variant, /*factored=*/1, stream);
+                          o_ss, status, variant, /*factored=*/1, stream, /*gamma_k_full=*/nullptr, /*after_prepare=*/true);
 }
 
 }  // extern "C"

@@ -54,6 +54,9 @@ __global__ void __launch_bounds__(kPrepThreads, KF_PREP_MINBLK) prepare_rows_ker
     constexpr int RPW = 32 / LPR;                    // rows per warp
     constexpr int RPB = RPW * (kPrepThreads / 32);   // positions per CTA
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // an attention kernel launched as a programmatic dependent may start its own prologue now; it reads the
+    // rows written here only after its griddepcontrol.wait
+    grid_dep_launch_dependents();
     const int sub = lane % LPR;                      // chunk index within the half row
     const int pos = blockIdx.x * RPB + warp * RPW + lane / LPR;
     const bool valid = pos < a.S;

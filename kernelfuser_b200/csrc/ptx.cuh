@@ -106,6 +106,12 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, const void* s
         ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
         : "memory");
 }
+// Programmatic dependent launch.  `grid_dep_launch_dependents` lets a grid that was launched with the
+// programmatic-serialisation attribute start before this grid has finished; `grid_dep_wait` in that grid
+// returns once the grid before it has completed and its writes are visible.  Both are no-ops in grids that are
+// launched the ordinary way.
+__device__ __forceinline__ void grid_dep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_read() {
