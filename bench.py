@@ -215,6 +215,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--variant", type=int, default=0)
     ap.add_argument("--batch", type=int, default=0, help="override the workload batch (profiling on a smaller case)")
+    ap.add_argument("--seq", type=int, default=0, help="override the workload sequence length (profiling only)")
     ap.add_argument("--no-graph", action="store_true", help="skip the graph-replay protocol")
     ap.add_argument("--sustained-s", type=float, default=2.5, help="seconds of back-to-back steps (0 = skip)")
     args = ap.parse_args()
@@ -224,6 +225,9 @@ def main():
     if args.batch > 0:
         import dataclasses
         w = dataclasses.replace(w, B=args.batch, name=f"{w.name}(batch {args.batch})")
+    if args.seq > 0:
+        import dataclasses
+        w = dataclasses.replace(w, S=args.seq, name=f"{w.name}(S {args.seq})")
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
