@@ -38,6 +38,14 @@ template <int D> __host__ __device__ constexpr int ws1_smem_bytes(bool factored 
     return ws1_q_bytes<D>() + 2 * kW256Stages * ws1_kv_tile_bytes<D>() + 1024 + 512 + (factored ? 512 : 0);
 }
 
+#ifdef KF_DEBUG
+// per-CTA phase stamps of thread 0 (SM clock), debug builds only
+__device__ long long g_w1_time[8192 * 8];
+#define KF_W1_STAMP(i) do { if (threadIdx.x == 0 && blockIdx.x < 8192) g_w1_time[blockIdx.x * 8 + (i)] = clock64(); } while (0)
+#else
+#define KF_W1_STAMP(i) do {} while (0)
+#endif
+
 template <int D, typename T, bool FACTORED = false>  // FACTORED: see attn_fwd_ws_kernel
 __global__ void __launch_bounds__(kW256Threads, (D == 128 ? 2 : 1))
 attn_fwd_ws1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -58,7 +66,9 @@ attn_fwd_ws1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 
     // An earlier CTA or launch failed: drain quickly.  One thread reads the word and the whole CTA follows that
     // reading, so no warp can leave while others go on to barriers the leaver would have served.
+    KF_W1_STAMP(0);
     if (__syncthreads_or(threadIdx.x == 0 && *reinterpret_cast<volatile int*>(a.status) != 0)) return;
+    KF_W1_STAMP(1);
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -131,6 +141,7 @@ attn_fwd_ws1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    KF_W1_STAMP(2);
 
     int fail = 0;
     int kv_issued = 0;  // producer bookkeeping for the exit path
@@ -142,7 +153,11 @@ attn_fwd_ws1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         const int row = m0 + r;
         {
             // (all lanes of a warp wait together; the vote keeps them together if the wait runs out)
-            auto wait_q = [&]() { return __all_sync(0xffffffffu, mbar_wait_abortable(q_full, 0, s_abort)) != 0; };
+            auto wait_q = [&]() {
+                const bool okq = __all_sync(0xffffffffu, mbar_wait_abortable(q_full, 0, s_abort)) != 0;
+                KF_W1_STAMP(7);
+                return okq;
+            };
             bool ok;
             if constexpr (FACTORED) ok = q_inv_coop<D, T>(smem_q, r, a, s_inv, wait_q);
             else ok = a.fuse_q ? q_prologue_coop<D, T, 4>(smem_q, r, m0, a, wait_q) : wait_q();
@@ -187,12 +202,14 @@ attn_fwd_ws1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         const float inv_c = 1.f / c;
         PolyBase pb;
         pb.set(0.f, inv_c);
+        KF_W1_STAMP(3);
         for (int jj = 0; jj < n_sub && !fail; ++jj) {
             const int buf = jj & 1;
             const int n0 = jj * kSub;
             const uint32_t col_sb = buf * kSub;
             if (!mbar_wait_abortable(s_full + buf, (jj >> 1) & 1, s_abort)) { fail = kStatusWsSFull; break; }
             tc_fence_after();
+            if (jj == 0) KF_W1_STAMP(4);
             uint32_t sr[2][32];
             tmem_ld32(lane_base + col_sb, sr[0]);
             tmem_ld32(lane_base + col_sb + 32, sr[1]);
@@ -271,6 +288,7 @@ attn_fwd_ws1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             __syncwarp();
             if (lane == 0) mbar_arrive(p_ready + buf);
         }
+        KF_W1_STAMP(5);
         // ---- epilogue: O / den -> 16-bit -> swizzled smem (the Q buffer) -> TMA store
         if (!fail && n_sub > 0 &&
             !mbar_wait_abortable(pv_done + ((n_sub - 1) & 1), ((n_sub - 1) >> 1) & 1, s_abort)) fail = kStatusWsODone;
@@ -309,6 +327,7 @@ attn_fwd_ws1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             tma_store_commit();
             tma_store_wait_read();  // the buffer must outlive the copy's reads; the writes drain on their own
         }
+        KF_W1_STAMP(6);
     } else if (warp == 4) {
         // =================================================== TMA producer
         if (elect_one()) {

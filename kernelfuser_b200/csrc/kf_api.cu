@@ -22,6 +22,9 @@
 extern "C" int kf_debug_read(int* host_out) {
     return (int)cudaMemcpyFromSymbol(host_out, kf::g_ps_dbg, sizeof(int) * 148 * 16 * 4);
 }
+extern "C" int kf_debug_w1(long long* host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, kf::g_w1_time, sizeof(long long) * 8192 * 8);
+}
 extern "C" int kf_debug_time(long long* host_out) {
     return (int)cudaMemcpyFromSymbol(host_out, kf::g_ps_time, sizeof(long long) * 148 * 16 * 8);
 }
