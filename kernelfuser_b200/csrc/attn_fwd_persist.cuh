@@ -490,6 +490,9 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                     ++kv_issued;
                     if (++s == kPsRing) { s = 0; epar ^= 1; }
                 };
+                // K is the output of the row-prepare launched just before this kernel: when this grid was launched
+                // as its programmatic dependent, the first K copy waits here for the prepare to complete
+                grid_dep_wait();
                 for (int n = 0; !fail; ++n) {
                     const int idx = ps_take_item<false>(c, n, 0, fail);
                     if (idx < 0) break;

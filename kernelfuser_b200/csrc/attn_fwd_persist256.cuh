@@ -426,6 +426,8 @@ attn_fwd_persist256_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                     ++kv_issued;
                     if (++s == kP2Ring) { s = 0; epar ^= 1; }
                 };
+                // (see attn_fwd_persist.cuh: the first K copy waits for the row-prepare this grid may depend on)
+                grid_dep_wait();
                 for (int n = 0; !fail; ++n) {
                     const int idx = p2_take_item<false>(c, n, 0, fail);
                     if (idx < 0) break;

@@ -242,6 +242,9 @@ constexpr long long kInterleaveMaxCtasPerSlot = 10;
 #define KF_DEPENDENT_MAX_TILES (1LL << 40)
 #endif
 constexpr long long kDependentMaxTiles = KF_DEPENDENT_MAX_TILES;
+#ifndef KF_DEPENDENT_PERSIST
+#define KF_DEPENDENT_PERSIST 1
+#endif
 
 // Sub-blocks of work per SM from which variant 0 picks the persistent kernel at D = 256.
 constexpr long long kPersist256MinSubBlocksPerSm = 200;
@@ -289,7 +292,7 @@ int sched_slot(unsigned int** out) {
 
 template <typename T>
 int launch_attn_persist(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
-                        const kf::AttnArgs& a0, cudaStream_t st) {
+                        const kf::AttnArgs& a0, cudaStream_t st, bool dependent = false) {
     auto kern = kf::attn_fwd_persist_kernel<T>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kf::kPsSmemBytes);
     if (e != cudaSuccess) return fail(KF_ECUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
@@ -301,15 +304,15 @@ int launch_attn_persist(const CUtensorMap& mq, const CUtensorMap& mk, const CUte
     const long long items = upg * a.B * a.Hkv;
     if (items > 0x7fffffffLL) return fail(KF_EINVAL, "too many tiles");
     const int grid = (int)(items < sm_count() ? items : sm_count());
-    e = launch_kernel(kern, dim3((unsigned)grid), dim3(kf::kPsThreads), (size_t)kf::kPsSmemBytes, st, mq, mk, mv, mo, a,
-                      (int)items);
+    e = launch_kernel_ex(kern, dim3((unsigned)grid), dim3(kf::kPsThreads), (size_t)kf::kPsSmemBytes, st, dependent, mq, mk, mv,
+                         mo, a, (int)items);
     if (e != cudaSuccess) return fail(KF_ECUDA, "attention launch failed: %s", cudaGetErrorString(e));
     return KF_OK;
 }
 
 template <typename T>
 int launch_attn_persist256(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const kf::AttnArgs& a0,
-                           cudaStream_t st) {
+                           cudaStream_t st, bool dependent = false) {
     auto kern = kf::attn_fwd_persist256_kernel<T>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kf::kP2SmemBytes);
     if (e != cudaSuccess) return fail(KF_ECUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
@@ -319,7 +322,8 @@ int launch_attn_persist256(const CUtensorMap& mq, const CUtensorMap& mk, const C
     const long long items = n_mblk * a.B * a.Hq;
     if (items > 0x7fffffffLL) return fail(KF_EINVAL, "too many tiles");
     const int grid = (int)(items < sm_count() ? items : sm_count());
-    e = launch_kernel(kern, dim3((unsigned)grid), dim3(kf::kP2Threads), (size_t)kf::kP2SmemBytes, st, mq, mk, mv, a, (int)items);
+    e = launch_kernel_ex(kern, dim3((unsigned)grid), dim3(kf::kP2Threads), (size_t)kf::kP2SmemBytes, st, dependent, mq, mk, mv, a,
+                         (int)items);
     if (e != cudaSuccess) return fail(KF_ECUDA, "attention launch failed: %s", cudaGetErrorString(e));
     return KF_OK;
 }
@@ -432,8 +436,8 @@ int attention_impl(const void* q, const void* kn, const void* v, const void* gam
         CUtensorMap mk64, mv64;  // the persistent kernel streams K/V in 64-row tiles
         if (int r = make_map(&mk64, kn, dtype, B, Hkv, S, D, k_sb, k_sh, k_ss, 64)) return r;
         if (int r = make_map(&mv64, v, dtype, B, Hkv, S, D, v_sb, v_sh, v_ss, 64)) return r;
-        return dtype == KF_BF16 ? launch_attn_persist<__nv_bfloat16>(mq, mk64, mv64, mo, a, st)
-                                : launch_attn_persist<__half>(mq, mk64, mv64, mo, a, st);
+        return dtype == KF_BF16 ? launch_attn_persist<__nv_bfloat16>(mq, mk64, mv64, mo, a, st, dependent && KF_DEPENDENT_PERSIST)
+                                : launch_attn_persist<__half>(mq, mk64, mv64, mo, a, st, dependent && KF_DEPENDENT_PERSIST);
     }
     {
         // CTA order (sg_decode).  Small launches - up to about ten CTAs per resident slot - interleave all
@@ -498,8 +502,8 @@ int attention_impl(const void* q, const void* kn, const void* v, const void* gam
         CUtensorMap mk64, mv64;  // K/V stream in 64-row tiles
         if (int r = make_map(&mk64, kn, dtype, B, Hkv, S, D, k_sb, k_sh, k_ss, 64)) return r;
         if (int r = make_map(&mv64, v, dtype, B, Hkv, S, D, v_sb, v_sh, v_ss, 64)) return r;
-        return dtype == KF_BF16 ? launch_attn_persist256<__nv_bfloat16>(mq, mk64, mv64, a, st)
-                                : launch_attn_persist256<__half>(mq, mk64, mv64, a, st);
+        return dtype == KF_BF16 ? launch_attn_persist256<__nv_bfloat16>(mq, mk64, mv64, a, st, dependent && KF_DEPENDENT_PERSIST)
+                                : launch_attn_persist256<__half>(mq, mk64, mv64, a, st, dependent && KF_DEPENDENT_PERSIST);
     }
     if (D == 256 && (variant == 0 || variant == 2)) {
         CUtensorMap mk64, mv64;  // K/V stream in 64-row tiles
