@@ -235,15 +235,14 @@ def launch_attention(inputs, out, *, causal=False, mode="query", bm=64, bn=64, w
     q, k, v, gq, gk, cos, sin = inputs
     if not rope:
         cos = sin = None
+    if mode != "full" and (kn is None or (mode == "unfused" and qn is None)):
+        raise ValueError("Missing scratch buffers")
     if not all(t.is_cuda for t in (q, k, v, gq, gk, out)):
         raise ValueError("Expected CUDA tensors")  # there is no CPU path
-    if mode == "full":
-        _check_strided(q, k, v)
     style = "hf" if hf_norm else "legacy"
     if mode == "full":
+        _check_strided(q, k, v)
         return attention_full(q, k, v, gq, gk, cos, sin, out, causal=causal, norm_style=style)
-    if kn is None or (mode == "unfused" and qn is None):
-        raise ValueError("Missing scratch buffers")
     prepare_rows(k, gk, cos, sin, norm_style=style, out=kn)
     if mode == "unfused":
         prepare_rows(q, gq, cos, sin, norm_style=style, out=qn)

@@ -144,6 +144,10 @@ def test_misuse_raises_value_error():
         kf.launch_attention((q, k, v, gq, gk, cos, sin), torch.empty_like(q), mode="key")
     with pytest.raises(ValueError, match="CUDA"):
         kf.launch_attention((q, k, v, gq, gk, cos, sin), torch.empty_like(q), mode="full")
+    with pytest.raises(ValueError, match="Missing scratch"):
+        kf.launch_attention((q, k, v, gq, gk, cos, sin), torch.empty_like(q), mode="query")
+    with pytest.raises(ValueError, match="Missing scratch"):
+        kf.launch_attention((q, k, v, gq, gk, cos, sin), torch.empty_like(q), mode="unfused", kn=torch.empty_like(k))
     # the arm adapter: unknown output layout, and CPU tensors
     with pytest.raises(ValueError, match="out_layout"):
         kf.fused(q, k, v, gq, gk, cos, sin, True, out_layout="sbhd")
