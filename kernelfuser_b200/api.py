@@ -243,11 +243,19 @@ def launch_attention(inputs, out, *, causal=False, mode="query", bm=64, bn=64, w
     if mode == "full":
         _check_strided(q, k, v)
         return attention_full(q, k, v, gq, gk, cos, sin, out, causal=causal, norm_style=style)
-    prepare_rows(k, gk, cos, sin, norm_style=style, out=kn)
     if mode == "unfused":
+        prepare_rows(k, gk, cos, sin, norm_style=style, out=kn)
         prepare_rows(q, gq, cos, sin, norm_style=style, out=qn)
         return attention_forward(qn, kn, v, gq, cos, sin, out, causal=causal, norm_style=style, fuse_q=False)
-    return attention_forward(q, kn, v, gq, cos, sin, out, causal=causal, norm_style=style, fuse_q=True)
+    # both launches in one C call (the attention kernel then starts as a dependent of the prepare)
+    b, hq, s, d = q.shape
+    with torch.cuda.device(q.device):
+        _call(_lib.load().kf_optimized_attention(
+            _ptr(q), _ptr(k), _ptr(v), _ptr(gq), _ptr(gk), _ptr(cos), _ptr(sin), _ptr(kn), _ptr(out),
+            b, hq, k.shape[1], s, d, _DTYPES[q.dtype], int(bool(causal)), int(bool(hf_norm)), 1e-6, float(d ** -0.5),
+            *_strides3(q), *_strides3(k), *_strides3(v), *_strides3(kn), *_strides3(out),
+            status_word(q.device).data_ptr(), _default_variant(), torch.cuda.current_stream().cuda_stream))
+    return out
 
 
 def fused(q, k, v, gq, gk, cos, sin, causal, eps=1e-6, scale=None, norm_style="qwen3", *, out_layout="bhsd"):
