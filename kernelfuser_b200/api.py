@@ -291,10 +291,15 @@ def fused(q, k, v, gq, gk, cos, sin, causal, eps=1e-6, scale=None, norm_style="q
     else:
         flat = out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
     kn = torch.empty(k.shape, dtype=k.dtype, device=k.device)
+    gq, gk = gq.contiguous(), gk.contiguous()
+    sc = float(d ** -0.5 if scale is None else scale)
     with torch.cuda.device(q.device):
-        prepare_rows(k, gk.contiguous(), cos, sin, norm_style=style, eps=eps, out=kn)
-        attention_forward(q, kn, v, gq.contiguous(), cos, sin, out, causal=causal, norm_style=style,
-                          fuse_q=True, eps=eps, scale=scale)
+        # both launches in one C call (the attention kernel then starts as a dependent of the prepare)
+        _call(_lib.load().kf_optimized_attention(
+            _ptr(q), _ptr(k), _ptr(v), _ptr(gq), _ptr(gk), _ptr(cos), _ptr(sin), _ptr(kn), _ptr(out),
+            b, hq, k.shape[1], s, d, _DTYPES[q.dtype], int(bool(causal)), int(style == "hf"), float(eps), sc,
+            *_strides3(q), *_strides3(k), *_strides3(v), *_strides3(kn), *_strides3(out),
+            status_word(q.device).data_ptr(), _default_variant(), torch.cuda.current_stream().cuda_stream))
     return flat
 
 
